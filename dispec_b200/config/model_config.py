@@ -184,11 +184,12 @@ def read_config_json(path: str) -> dict:
 
 
 def load_model_config(path_or_dict) -> ModelConfig:
-    """Choose the configuration class by ``architectures[0]`` through the registry."""
+    """Choose the configuration class through the registry, by ``architectures[0]`` or, in files
+    that name one architecture as a string, by ``architecture``."""
     from dispec_b200.registry import architecture_entry
 
     d = path_or_dict if isinstance(path_or_dict, dict) else read_config_json(path_or_dict)
-    archs = d.get("architectures")
+    archs = d.get("architectures") or ([d["architecture"]] if isinstance(d.get("architecture"), str) else None)
     if not archs:
-        raise ConfigError("config.json lacks 'architectures'")
+        raise ConfigError("config.json lacks 'architectures' (or 'architecture')")
     return architecture_entry(archs[0]).config_class.from_dict(d)

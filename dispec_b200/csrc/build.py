@@ -26,6 +26,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CORE_SOURCES = [
     "runtime.cu",
     "elementwise.cu",
+    "norm32.cu",
     "gemm_simt.cu",
     "gemm_tcgen05.cu",
     "gemm_stream.cu",
@@ -160,6 +161,7 @@ def build_all(head_dims=(16, 32, 64, 128)) -> list[str]:
         libs.append(attention_library(d))
         if d in (64, 128):
             libs.append(prefill_attention_library(d))
+    libs += [mixer_library(name) for name in MIXER_LIBRARIES]
     return libs
 
 
@@ -169,6 +171,15 @@ def attention_library(head_dim: int) -> str:
 
 def prefill_attention_library(head_dim: int) -> str:
     return specialised_library(f"attn_tcgen05_d{head_dim}", "attn_tcgen05.cu", {"DSP_HEAD_DIM": head_dim})
+
+
+# Kernels only some mixers need, each a library of its own that is built when a model with such
+# a mixer first runs: name -> source file.
+MIXER_LIBRARIES = {"linear_recurrence": "linear_recurrence.cu", "attn_latent": "attn_latent.cu"}
+
+
+def mixer_library(name: str) -> str:
+    return specialised_library(name, MIXER_LIBRARIES[name], {})
 
 
 if __name__ == "__main__":

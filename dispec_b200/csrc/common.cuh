@@ -110,6 +110,19 @@ template <typename T> __device__ __forceinline__ T from_f32(float v);
 template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16(v); }
 
+// Loads and stores through a type code (DSP_F32 / DSP_BF16), for memory-bound kernels whose
+// operands come in either type independently of one another.
+__device__ __forceinline__ float ld_any(const void* p, int dtype, size_t i) {
+  return dtype == DSP_F32 ? reinterpret_cast<const float*>(p)[i]
+                          : __bfloat162float(reinterpret_cast<const bf16*>(p)[i]);
+}
+__device__ __forceinline__ void st_any(void* p, int dtype, size_t i, float v) {
+  if (dtype == DSP_F32)
+    reinterpret_cast<float*>(p)[i] = v;
+  else
+    reinterpret_cast<bf16*>(p)[i] = __float2bfloat16(v);
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

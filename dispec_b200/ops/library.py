@@ -61,6 +61,16 @@ def prefill_attention_library(head_dim: int) -> ctypes.CDLL:
     return _special[key]
 
 
+def mixer_library(name: str) -> ctypes.CDLL:
+    """A library of kernels that only some mixers need (``build.MIXER_LIBRARIES``)."""
+    if name not in _special:
+        core()  # the runtime's symbols (error word, messages) come from the core library
+        with _lock:
+            if name not in _special:
+                _special[name] = ctypes.CDLL(build.mixer_library(name))
+    return _special[name]
+
+
 def loaded_libraries() -> list[str]:
     out = [] if _core is None else [_core._name]
     return out + [lib._name for lib in _special.values()]

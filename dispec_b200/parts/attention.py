@@ -82,6 +82,8 @@ class GQAAttention(Mixer):
         H, KVH, D = self.num_heads, self.num_kv_heads, self.head_dim
         qkv = ops.linear(x, self.w_qkv, self.b_qkv)
         rot = self.position_encoding.rotation()
+        if rot is not None and rot.layout != "halves":
+            raise ValueError(f"gqa_attention turns pairs (i, i + rotary_dim/2) only, not the {rot.layout!r} layout")
         inv_freq, rotary_dim = (rot.inv_freq, rot.rotary_dim) if rot is not None else (None, 0)
         scale = self.scale * self.position_encoding.score_scale()
         # single tokens come first in the batch: when their attention kernel rotates q and k itself and

@@ -78,6 +78,20 @@ class StateNeed:
     dtype: str = "float32"
 
 
+@dataclass
+class WideStream:
+    """A residual stream kept in 32-bit floats (``full``, [T, width]) beside the copy rounded to
+    the model type that the products read (``rounded``; the same tensor on the 32-bit path).
+    Blocks that keep the stream this way pass it on as their ``x``; a norm that takes it
+    (``rms_norm_f32``) reads ``full``."""
+    full: torch.Tensor
+    rounded: torch.Tensor
+
+    @property
+    def shape(self):
+        return self.full.shape
+
+
 class Part:
     role = ""
     kind = ""
@@ -103,10 +117,12 @@ class Norm(Part):
 
 @dataclass(frozen=True)
 class Rotation:
-    """Rotation of query and key heads: the pair (i, i + rotary_dim/2) of every head is turned
-    by the angle position * inv_freq[i]; dimensions from ``rotary_dim`` on pass unchanged."""
+    """Rotation of query and key heads: pair i of every head is turned by the angle
+    position * inv_freq[i]; dimensions from ``rotary_dim`` on pass unchanged.  ``layout`` says
+    which dimensions form pair i: "halves" (i, i + rotary_dim/2) or "interleaved" (2i, 2i+1)."""
     inv_freq: Any  # float32 [rotary_dim / 2] on the device
     rotary_dim: int
+    layout: str = "halves"
 
 
 class PositionEncoding(Part):

@@ -9,7 +9,7 @@ adds it."""
 from __future__ import annotations
 
 from dispec_b200.ops.gemm import NormedRows
-from dispec_b200.parts.base import Block
+from dispec_b200.parts.base import Block, WideStream
 from dispec_b200.registry import register_part
 
 
@@ -67,3 +67,37 @@ class PreNormBlock(Block):
         a = self.mixer.forward(ctx, h, cache, state)
         h = self.ffn_norm.forward_add(ctx, x, a)
         return x, self.feed_forward.forward(ctx, h)
+
+
+@register_part("block", "post_norm")
+class PostNormBlock(Block):
+    """Norm after the sum:
+
+        x <- norm1(alpha * x + mixer(x));   x <- norm2(alpha * x + ffn(x))
+
+    The sublayers read x itself (the normalised stream).  The stream is kept in 32-bit floats
+    (``WideStream``): sum and norm are formed in 32-bit from the 32-bit stream and the sublayer's
+    32-bit result, and a copy rounded to the model type is written beside it for the products.
+    ``feed_forward`` (with ``ffn_norm``) may be None: the layer then has the first sublayer only.
+    The norms must offer ``scaled_sum`` (``rms_norm_f32``)."""
+
+    def __init__(self, mixer_norm, mixer, alpha: float, ffn_norm=None, feed_forward=None):
+        if (ffn_norm is None) != (feed_forward is None):
+            raise ValueError("post_norm: a feed-forward and its norm come together or not at all")
+        for norm in (mixer_norm, ffn_norm):
+            if norm is not None and not hasattr(norm, "scaled_sum"):
+                raise ValueError(f"post_norm: the norm {type(norm).__name__} cannot take a scaled sum")
+        self.mixer_norm = mixer_norm
+        self.mixer = mixer
+        self.ffn_norm = ffn_norm
+        self.feed_forward = feed_forward
+        self.alpha = float(alpha)
+
+    def forward(self, ctx, x, pending, cache, state):
+        if pending is not None:
+            raise ValueError("post_norm: nothing can be pending in front of this block")
+        h = x.rounded if isinstance(x, WideStream) else x
+        x = self.mixer_norm.scaled_sum(ctx, x, self.mixer.forward(ctx, h, cache, state), self.alpha)
+        if self.feed_forward is not None:
+            x = self.ffn_norm.scaled_sum(ctx, x, self.feed_forward.forward(ctx, x.rounded), self.alpha)
+        return x, None

@@ -4,9 +4,12 @@ borrowed module was measured to use; applied at puneethgv/DiSpec
 dispec/engine/model_runner.py:215,218,220)."""
 from __future__ import annotations
 
+import torch
+
 from dispec_b200 import ops
 from dispec_b200.ops import gemm as gemm_ops
-from dispec_b200.parts.base import Norm, TensorSpec
+from dispec_b200.ops import norm32 as norm32_ops
+from dispec_b200.parts.base import Norm, TensorSpec, WideStream
 from dispec_b200.registry import register_part
 
 
@@ -39,3 +42,40 @@ class RMSNorm(Norm):
         """Norm of residual + delta (32-bit sum).  Without ``rows`` the sum replaces ``residual``."""
         return ops.rms_norm(residual, self.weight, self.eps, delta=delta, rows=rows,
                             write_back=rows is None)
+
+
+@register_part("norm", "rms_norm_f32")
+class RMSNorm32(Norm):
+    """y = w * x / sqrt(mean(x^2) + eps), everything in 32-bit: the gain is kept as float32 in
+    every mode and nothing is rounded before the result.  Reads a 32-bit stream (``WideStream``)
+    or a plain tensor of either type.  ``forward`` returns the result in ``ctx.dtype`` (what a
+    product reads); ``scaled_sum`` is the norm of alpha * x + delta, returned as a new
+    ``WideStream`` (the arrangement with the norm after the sum)."""
+
+    def __init__(self, hidden_size: int, eps: float):
+        self.hidden_size = hidden_size
+        self.eps = eps
+        self.weight = None
+
+    def tensor_specs(self):
+        return {"weight": TensorSpec((self.hidden_size,), dtype="float32", init="one_plus_normal")}
+
+    def load(self, tensors):
+        self.weight = tensors["weight"]
+
+    @staticmethod
+    def _full(x):
+        return x.full if isinstance(x, WideStream) else x
+
+    def forward(self, ctx, x, rows=None):
+        return norm32_ops.sum_norm(self._full(x), self.weight, self.eps, rows=rows, out_dtype=ctx.dtype,
+                                   want32=False)[1]
+
+    def scaled_sum(self, ctx, x, delta, alpha: float) -> WideStream:
+        """Norm of alpha * x + delta (32-bit sum).  The 32-bit result replaces ``x.full`` when x
+        is a stream of this model's own making."""
+        src = self._full(x)
+        into = src if isinstance(x, WideStream) and src.dtype == torch.float32 else None
+        full, rounded = norm32_ops.sum_norm(src, self.weight, self.eps, delta=delta, alpha=alpha,
+                                            out32=into, out_dtype=ctx.dtype)
+        return WideStream(full, rounded)

@@ -1,5 +1,7 @@
 """Rotary position encoding, "default" type: inv_freq[i] = theta^(-2i/rotary_dim), angle =
-position * inv_freq[i] in 32-bit, pairs (i, i + rotary_dim/2) rotated (half-split layout).
+position * inv_freq[i] in 32-bit, pairs (i, i + rotary_dim/2) rotated (half-split layout, the
+default) or pairs (2i, 2i+1) (``layout="interleaved"``); the mixer that consumes the rotation
+says which layouts its kernels turn.
 puneethgv/DiSpec dispec/engine/model_runner.py:35-44,121-124; the table formula in 32-bit at
 dispec/kv/transfer.py:50-58.  The reference rounds the cos/sin tables to the model type and
 rotates in that type; here angles, cos, sin and the rotation are 32-bit and the result is
@@ -14,7 +16,10 @@ from dispec_b200.registry import register_part
 
 @register_part("position_encoding", "rotary")
 class RotaryEncoding(PositionEncoding):
-    def __init__(self, head_dim: int, theta: float, rotary_dim: int | None = None):
+    def __init__(self, head_dim: int, theta: float, rotary_dim: int | None = None, layout: str = "halves"):
+        if layout not in ("halves", "interleaved"):
+            raise ValueError(f"rotary layout {layout!r} is not one of 'halves', 'interleaved'")
+        self.layout = layout
         self.head_dim = head_dim
         self.theta = float(theta)
         self.rotary_dim = head_dim if rotary_dim is None else rotary_dim
@@ -29,7 +34,7 @@ class RotaryEncoding(PositionEncoding):
     def rotation(self):
         if self.inv_freq is None:
             raise RuntimeError("the rotary encoding was not prepared (load the model first)")
-        return Rotation(self.inv_freq, self.rotary_dim)
+        return Rotation(self.inv_freq, self.rotary_dim, self.layout)
 
 
 @register_part("position_encoding", "none")
