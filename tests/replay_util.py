@@ -111,7 +111,7 @@ class Trace:
 
 
 def run_trace(model_dir, dtype, trace, max_tokens, out_dir, page_size=16, poison=True, timeout=600,
-              cuda_graph=False):
+              cuda_graph=False, max_requests=None):
     """Runs bin/trace_run on the trace; returns {(step, request, position): logits row}."""
     cmd = [sys.executable, TRACE_RUN, "--model", model_dir, "--dtype", dtype, "--out", out_dir,
            "--max-tokens", str(max_tokens), "--page-size", str(page_size)]
@@ -119,6 +119,8 @@ def run_trace(model_dir, dtype, trace, max_tokens, out_dir, page_size=16, poison
         cmd.append("--poison-freed-pages")
     if cuda_graph:
         cmd.append("--cuda-graph")
+    if max_requests is not None:
+        cmd += ["--max-requests", str(max_requests)]
     text = "".join(json.dumps(s) + "\n" for s in trace.steps)
     proc = subprocess.run(cmd, input=text, capture_output=True, text=True, timeout=timeout)
     if proc.returncode != 0:
