@@ -497,6 +497,117 @@ def decode_timeline(args) -> dict:
             "products": {k: v[-1] for k, v in products.items()}, "attention": attention[-1] if attention else None}
 
 
+# ------------------------------------------------------------ Puludra beside Qwen2 at equal size
+# Layer sizes that resemble real models of the two families at the same width, depth, vocabulary
+# and feed-forward width: eight layers each (a period of the mixers twice); the Qwen2 arm is the
+# recorded configuration cut to the same depth.
+PULUDRA_SHAPES = {
+    "1.5b": dict(width=1536, heads=12, dim=128, vdim=128, rot_dim=64, kv_rank=512, q_rank=768, ff=8960, vocab=151936),
+    "7b": dict(width=3584, heads=28, dim=128, vdim=128, rot_dim=64, kv_rank=512, q_rank=1536, ff=18944, vocab=152064),
+}
+PULUDRA_LAYERS = 8
+
+
+def puludra_config(shape: str) -> dict:
+    z = PULUDRA_SHAPES[shape]
+    H, d, dv = z["heads"], z["dim"], z["vdim"]
+    mlp = {"kind": "dense", "ff": z["ff"]}
+    att = {"type": "latent_attention", "mlp": mlp,
+           "mixer": {"heads": H, "dim": d, "rot_dim": z["rot_dim"], "vdim": dv, "kv_rank": z["kv_rank"],
+                     "q_rank": z["q_rank"], "scale": (d + z["rot_dim"]) ** -0.5,
+                     "rot": {"base": 1e6, "dims": z["rot_dim"]}}}
+    ret = {"type": "retention", "mlp": mlp,
+           "mixer": {"heads": H, "dim": d, "vdim": dv, "decay": [1 - 2.0 ** (-5 - 3 * i / max(H - 1, 1)) for i in range(H)],
+                     "rot": {"base": 1e6, "dims": d}}}
+    hg = {"type": "hgrn2", "mlp": mlp, "mixer": {"heads": H, "dim": d, "vdim": dv}}
+    return {"architecture": "Puludra", "vocab": z["vocab"], "width": z["width"], "postln_alpha": 2.0,
+            "norm": {"eps": 1e-6}, "layers": [ret, att, hg, att] * (PULUDRA_LAYERS // 4)}
+
+
+def puludra_bytes_and_flops(cfg: dict):
+    W, V = cfg["width"], cfg["vocab"]
+    weights = V * W * 2 + W  # embedding row gather is negligible; head read once, final norm
+    per_token_cache, state_bytes, matmul, attn_per_tt, rec_per_t = 0, 0, 0, 0, 0
+    for e in cfg["layers"]:
+        m = e["mixer"]
+        H, d, dv = m["heads"], m["dim"], m["vdim"]
+        if e["type"] == "latent_attention":
+            r, R, Q = m["rot_dim"], m["kv_rank"], m["q_rank"]
+            n = (Q + R + r) * W + H * (d + r) * Q + H * d * R + H * dv * R + W * H * dv
+            per_token_cache += (R + r) * 2
+            attn_per_tt += H * (2 * R + r)  # scores and weighted sum over half of the T x T pairs, 2 flops each
+        elif e["type"] == "retention":
+            n = (2 * H * d + 2 * H * dv) * W + W * H * dv
+            state_bytes += 2 * H * d * dv * 4
+            rec_per_t += 4 * H * d * dv
+        else:
+            n = (2 * H * d + H * dv) * W + W * H * dv
+            state_bytes += 2 * H * d * dv * 4
+            rec_per_t += 4 * H * d * dv
+        if e.get("mlp"):
+            n += 2 * e["mlp"]["ff"] * W
+        matmul += n
+    weight_bytes = 2 * (matmul + V * W)
+
+    def prefill_flops(T):
+        return 2 * T * matmul + attn_per_tt * T * T + rec_per_t * T + 2 * V * W
+
+    return weight_bytes, per_token_cache, state_bytes, prefill_flops
+
+
+def puludra_points(args, pk: dict) -> dict:
+    """Prefill (2,048 tokens in one step) and decode (batch 1, 8, 64 at 1,024 tokens of context,
+    replayed from captured graphs) of Puludra and of Qwen2 at equal width, depth, vocabulary and
+    feed-forward width, each with the fraction of its own roofline (bytes a decode step must read
+    over the measured copy bandwidth; prefill FLOPs over the measured bf16 peak)."""
+    import torch
+    from dispec_b200 import load_model_config
+    from dispec_b200.engine import ModelRunner
+    from dispec_b200.weights import load_random_model
+    out = {"only": "puludra", "layers": PULUDRA_LAYERS, "prompt_len": PROMPT_LEN, "prefill_tokens": PREFILL_TOKENS,
+           "peaks": pk}
+    steps, warmup = max(20, min(args.steps, 50)), max(3, args.warmup // 2)
+    per_req = (PROMPT_LEN + NEW_TOKENS + steps + warmup + PAGE_SIZE) // PAGE_SIZE + 1
+    shapes = ["1.5b"] if args.no_other_shapes else list(PULUDRA_SHAPES)
+    for shape in shapes:
+        for family in ("puludra", "qwen2"):
+            if family == "puludra":
+                cfg_dict = puludra_config(shape)
+                weight_bytes, cache_per_token, state_bytes, prefill_flops = puludra_bytes_and_flops(cfg_dict)
+                vocab = cfg_dict["vocab"]
+            else:
+                cfg_dict = dict(BENCH_CONFIG)
+                if shape != "1.5b":
+                    cfg_dict.update(OTHER_SHAPES[shape][0])
+                cfg_dict["num_hidden_layers"] = PULUDRA_LAYERS
+                weight_bytes, cache_per_token, prefill_flops = model_bytes_and_flops(cfg_dict, PULUDRA_LAYERS)
+                state_bytes, vocab = 0, cfg_dict["vocab_size"]
+            model = load_random_model(load_model_config(cfg_dict), 5, STD, "bfloat16", "cuda:0")
+            torch.cuda.synchronize()
+            key = f"{family}_{shape}"
+            out[f"{key}_weight_gb"] = round(weight_bytes / 1e9, 3)
+            for b in (1, 8, 64):
+                r = ModelRunner(model, page_size=PAGE_SIZE, num_pages=max(b * per_req, 160), max_num_seqs=max(b, 8),
+                                cuda_graph=True)
+                ms, launches, ctx = decode_direct(r, random_prompts(b, PROMPT_LEN, vocab, 13 + b), steps, warmup)
+                step_bytes = weight_bytes + b * (ctx * cache_per_token + state_bytes)
+                out[f"{key}_decode_b{b}"] = round(b * 1000.0 / ms, 1)
+                out[f"{key}_decode_b{b}_ms"] = round(ms, 4)
+                out[f"{key}_decode_b{b}_hbm_frac"] = round(step_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+                out[f"{key}_decode_b{b}_launches_per_step"] = launches // steps
+                if b == 1:
+                    pms = prefill_time(r, random_prompts(1, PREFILL_TOKENS, vocab, 12)[0], repeats=3)
+                    out[f"{key}_prefill"] = round(PREFILL_TOKENS / pms * 1000.0, 1)
+                    out[f"{key}_prefill_ms"] = round(pms, 3)
+                    out[f"{key}_prefill_frac"] = round(prefill_flops(PREFILL_TOKENS) / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)
+                del r
+                torch.cuda.empty_cache()
+            del model
+            torch.cuda.empty_cache()
+            print(f"bench: {key} done", file=sys.stderr, flush=True)
+    return out
+
+
 def run_ours(args) -> dict:
     import torch
     from dispec_b200 import load_model_config
@@ -511,6 +622,8 @@ def run_ours(args) -> dict:
         return tma_ingest_rate()
     if args.only == "timeline":
         return decode_timeline(args)
+    if args.only == "puludra":
+        return puludra_points(args, peaks())
     cfg_dict = dict(BENCH_CONFIG)
     seed = SEED
     if args.shape != "1.5b":
@@ -680,12 +793,13 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (recorded)")
     ap.add_argument("--shape", choices=["1.5b", "7b", "14b"], default="1.5b",
                     help="layer sizes: Qwen2.5-1.5B (the default and the recorded configuration), 7B or 14B")
-    ap.add_argument("--only", choices=["decode", "prefill", "timeline", "mma-rate", "tma-rate", "attn-prefill"], default=None,
+    ap.add_argument("--only", choices=["decode", "prefill", "timeline", "mma-rate", "tma-rate", "attn-prefill", "puludra"], default=None,
                     help="profiling aid: run one phase only and print a short line; timeline: where the time of the "
                          "decode step's products and attention goes (a build with timestamps); mma-rate: cycles per "
                          "tcgen05.mma for one to four issuing threads; tma-rate: bytes a clock an SM takes in from "
                          "the L2 by TMA, by the size of a request; attn-prefill: the attention kernel for portions of prompts "
-                         "alone, by shape, length and the order of the pages")
+                         "alone, by shape, length and the order of the pages; puludra: prefill and decode of the Puludra design beside "
+                         "Qwen2 at equal width, depth, vocabulary and feed-forward width (eight layers each), with roofline fractions")
     ap.add_argument("--batch", type=int, default=BATCH, help="batch of the --only decode phase")
     ap.add_argument("--max-key-ranges", type=int, default=0,
                     help="profiling aid: cap on the key ranges per decoded row beyond one cluster (1: none)")

@@ -284,3 +284,331 @@ extern "C" int dsp_attn_latent(const float* qa, long ldqa, const void* q, int q_
 #undef DSP_LATENT_ARGS
   DSP_REQUIRE(false, "dsp_attn_latent: unknown pool dtype %d", pool_dtype);
 }
+
+// ------------------------------------------------------------------- tensor cores (bfloat16)
+// The same attention on mma.sync for bfloat16 pools: a CTA takes a tile of up to 64 query rows,
+// a row being a (token, head) pair of ONE request: TPT consecutive tokens of its portion times
+// HC heads (all of them up to 64).  Every head reads the same key row, so the tile shares each
+// key tile it loads among all its rows.  Keys come in tiles of 32 through the page table
+// (cp.async, two buffers); a key row is [latent R | rotated part r] in shared memory and its
+// first R values are the value row as well.  16 warps = 4 row groups x 4 column groups:
+//   S = Q K^T   warp (rg, cg) forms the 16 x 8 block of its rows and keys cg*8.. over the depth R + r
+//   softmax     row maxima and sums of the four column groups meet in shared memory; P goes there
+//               as bfloat16 (the sums are taken before the rounding)
+//   O += P V    warp (rg, cg) owns the R / 4 output columns cg * R/4 .. of its rows
+// The key tiles of a tile can be cut into `splits` ranges (grid.z), each leaving an unnormalised
+// partial and (maximum in the base-2 domain, sum) per row for dsp_attn_combine: single tokens
+// with long contexts then fill the device.  Keys beyond the tile's last position are never
+// loaded (zero rows); a page id outside the pool is recorded and its rows are zero.
+namespace tc {
+constexpr int BM = 64, BN = 32, THREADS = 512, P_ROWB = 80;
+
+struct Args {
+  const float* qa; long ldqa;
+  const void* q; int q_dtype; long ldq; int q_head_stride, qr_off;
+  const float* inv_freq; int rot;
+  const bf16* c_pool; const bf16* r_pool;
+  const int* page_table; int pt_stride;
+  const int* q_start; const int* ctx_len;
+  const int* tile_seq; const int* tile_tok0; int tile_offset;
+  bf16* out; long ldo;
+  float* part_o; float* part_ml; int splits;
+  int H, HC, TPT, R, r, page_size, num_pages;
+  float scale_log2;
+  int* err;
+};
+
+__device__ __forceinline__ void cp_async16(uint32_t smem, const void* gmem, bool valid) {
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x2(uint32_t (&r)[2], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__host__ __device__ inline int key_row_bytes(int W) { return ((W * 2 + 127) / 128) * 128 + 16; }
+
+// NT16: blocks of 16 output columns per warp = R / 64
+template <int NT16>
+__global__ void __launch_bounds__(THREADS, 1) attn_latent_mma_kernel(const Args p) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  const int W = p.R + p.r, ROWB = key_row_bytes(W), CH = W / 8, CH_LAT = p.R / 8;
+  const uint32_t q_s = (uint32_t)__cvta_generic_to_shared(smem);
+  const uint32_t k_s = q_s + BM * ROWB;
+  const uint32_t p_s = k_s + 2 * BN * ROWB;
+  float* red_max = reinterpret_cast<float*>(smem + (size_t)BM * ROWB + 2 * (size_t)BN * ROWB + BM * P_ROWB);  // [BM][4]
+  float* red_sum = red_max + BM * 4;                                                                          // [BM][4]
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int rg = warp & 3, cg = warp >> 2;
+  const int tile = blockIdx.x + p.tile_offset;
+  const int seq = p.tile_seq[tile], tok0 = p.tile_tok0[tile];
+  const int head0 = blockIdx.y * p.HC, hc = min(p.HC, p.H - head0);
+  const int qs = p.q_start[seq], qlen = p.q_start[seq + 1] - qs, clen = p.ctx_len[seq];
+  const int ntok = min(p.TPT, qlen - tok0), nrows = ntok * hc;
+  const int pos0 = clen - qlen + tok0;
+  if (clen <= 0 || pos0 < 0 || ntok <= 0) return;  // a padding row of a captured step
+  const int hi = pos0 + ntok - 1;
+  const int total = hi / BN + 1, per = (total + p.splits - 1) / p.splits;
+  const int kb = blockIdx.z * per, ke = min(total, kb + per);
+  const int* table = p.page_table + (size_t)seq * p.pt_stride;
+  const int g = lane >> 2, c4 = lane & 3, m8 = lane >> 3, l8 = lane & 7;
+  const int row_a = rg * 16 + g, row_b = row_a + 8;
+
+  if (kb >= ke) {  // a key range with nothing in it: says so to the merge
+    for (int m = tid; m < nrows; m += THREADS) {
+      const size_t row = (size_t)(qs + tok0 + m / hc) * p.H + head0 + m % hc;
+      p.part_ml[(row * p.splits + blockIdx.z) * 2] = -INFINITY;
+      p.part_ml[(row * p.splits + blockIdx.z) * 2 + 1] = 0.f;
+    }
+    return;
+  }
+
+  auto load_keys = [&](int kt, int buf) {
+    for (int c = tid; c < BN * CH; c += THREADS) {
+      const int row = c / CH, ch = c % CH;
+      const int key = kt * BN + row;
+      bool valid = key <= hi;
+      long at = 0;
+      if (valid) {
+        const int page = table[key / p.page_size];
+        if (page < 0 || page >= p.num_pages) {
+          atomicOr(p.err, DSP_ERR_BAD_PAGE);
+          valid = false;
+        } else {
+          at = (long)page * p.page_size + key % p.page_size;
+        }
+      }
+      const bf16* src = ch < CH_LAT ? p.c_pool + at * p.R + ch * 8 : p.r_pool + at * p.r + (ch - CH_LAT) * 8;
+      cp_async16(k_s + (buf * BN + row) * ROWB + ch * 16, src, valid);
+    }
+    cp_async_commit();
+  };
+  load_keys(kb, 0);
+
+  // the query rows as bfloat16: [absorbed query | rotated part], zero beyond the tile's rows
+  for (int idx = tid; idx < BM * (W / 2); idx += THREADS) {
+    const int m = idx / (W / 2), d = (idx % (W / 2)) * 2;
+    float v0 = 0.f, v1 = 0.f;
+    if (m < nrows) {
+      const int t = qs + tok0 + m / hc, hd = head0 + m % hc;
+      if (d < p.R) {
+        const float2 v = *reinterpret_cast<const float2*>(p.qa + (size_t)t * p.ldqa + (size_t)hd * p.R + d);
+        v0 = v.x;
+        v1 = v.y;
+      } else {
+        const int j = d - p.R;
+        const size_t at = (size_t)t * p.ldq + (size_t)hd * p.q_head_stride + p.qr_off;
+        v0 = ld_any(p.q, p.q_dtype, at + j);
+        v1 = ld_any(p.q, p.q_dtype, at + j + 1);
+        if (j < p.rot) {
+          float sn, cs;
+          sincosf((float)(pos0 + m / hc) * p.inv_freq[j >> 1], &sn, &cs);
+          const float u = v0, w = v1;
+          v0 = u * cs - w * sn;
+          v1 = w * cs + u * sn;
+        }
+      }
+    }
+    *reinterpret_cast<uint32_t*>(smem + (size_t)m * ROWB + d * 2) = pack_bf16(v0, v1);
+  }
+
+  float o[2 * NT16][4];
+#pragma unroll
+  for (int i = 0; i < 2 * NT16; ++i)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[i][e] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  const int pos_a = row_a < nrows ? pos0 + row_a / hc : -1, pos_b = row_b < nrows ? pos0 + row_b / hc : -1;
+
+  for (int kt = kb; kt < ke; ++kt) {
+    const int buf = (kt - kb) & 1;
+    if (kt + 1 < ke) {
+      load_keys(kt + 1, buf ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const uint32_t kbuf = k_s + buf * BN * ROWB;
+    float s[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int kk = 0; kk < W / 16; ++kk) {
+      uint32_t a[4], b[2];
+      ldmatrix_x4(a, q_s + (rg * 16 + (m8 & 1) * 8 + l8) * ROWB + (kk * 2 + (m8 >> 1)) * 16);
+      ldmatrix_x2(b, kbuf + (cg * 8 + l8) * ROWB + (kk * 2 + (m8 & 1)) * 16);
+      mma_bf16(s, a, b[0], b[1]);
+    }
+    const int key0 = kt * BN + cg * 8 + 2 * c4;
+    s[0] = key0 <= pos_a ? s[0] * p.scale_log2 : -INFINITY;
+    s[1] = key0 + 1 <= pos_a ? s[1] * p.scale_log2 : -INFINITY;
+    s[2] = key0 <= pos_b ? s[2] * p.scale_log2 : -INFINITY;
+    s[3] = key0 + 1 <= pos_b ? s[3] * p.scale_log2 : -INFINITY;
+    float tmax[2] = {fmaxf(s[0], s[1]), fmaxf(s[2], s[3])};
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 1));
+      tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 2));
+    }
+    if (c4 == 0) {
+      red_max[row_a * 4 + cg] = tmax[0];
+      red_max[row_b * 4 + cg] = tmax[1];
+    }
+    __syncthreads();
+    float alpha[2], m_safe[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const float4 mx = *reinterpret_cast<const float4*>(red_max + (r == 0 ? row_a : row_b) * 4);
+      const float m_new = fmaxf(m_run[r], fmaxf(fmaxf(mx.x, mx.y), fmaxf(mx.z, mx.w)));
+      m_safe[r] = (m_new == -INFINITY) ? 0.f : m_new;
+      alpha[r] = exp2f(m_run[r] - m_safe[r]);
+      m_run[r] = m_new;
+    }
+    const float p0 = exp2f(s[0] - m_safe[0]), p1 = exp2f(s[1] - m_safe[0]);
+    const float p2 = exp2f(s[2] - m_safe[1]), p3 = exp2f(s[3] - m_safe[1]);
+    float psum[2] = {p0 + p1, p2 + p3};
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      psum[r] += __shfl_xor_sync(0xffffffffu, psum[r], 1);
+      psum[r] += __shfl_xor_sync(0xffffffffu, psum[r], 2);
+    }
+    if (c4 == 0) {
+      red_sum[row_a * 4 + cg] = psum[0];
+      red_sum[row_b * 4 + cg] = psum[1];
+    }
+    unsigned char* pw = smem + (size_t)BM * ROWB + 2 * (size_t)BN * ROWB;
+    *reinterpret_cast<uint32_t*>(pw + row_a * P_ROWB + (cg * 8 + 2 * c4) * 2) = pack_bf16(p0, p1);
+    *reinterpret_cast<uint32_t*>(pw + row_b * P_ROWB + (cg * 8 + 2 * c4) * 2) = pack_bf16(p2, p3);
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const float4 sm = *reinterpret_cast<const float4*>(red_sum + (r == 0 ? row_a : row_b) * 4);
+      l_run[r] = l_run[r] * alpha[r] + ((sm.x + sm.y) + (sm.z + sm.w));
+    }
+#pragma unroll
+    for (int i = 0; i < 2 * NT16; ++i) {
+      o[i][0] *= alpha[0];
+      o[i][1] *= alpha[0];
+      o[i][2] *= alpha[1];
+      o[i][3] *= alpha[1];
+    }
+#pragma unroll
+    for (int j = 0; j < BN / 16; ++j) {
+      uint32_t a[4];
+      ldmatrix_x4(a, p_s + (rg * 16 + (m8 & 1) * 8 + l8) * P_ROWB + (j * 2 + (m8 >> 1)) * 16);
+#pragma unroll
+      for (int dd = 0; dd < NT16; ++dd) {
+        uint32_t b[4];
+        ldmatrix_x4_trans(b, kbuf + (j * 16 + (m8 & 1) * 8 + l8) * ROWB + ((cg * NT16 + dd) * 2 + (m8 >> 1)) * 16);
+        mma_bf16(o[2 * dd], a, b[0], b[1]);
+        mma_bf16(o[2 * dd + 1], a, b[2], b[3]);
+      }
+    }
+    __syncthreads();
+  }
+
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int m = r == 0 ? row_a : row_b;
+    if (m >= nrows) continue;
+    const int t = qs + tok0 + m / hc, hd = head0 + m % hc;
+    if (p.splits == 1) {
+      const float inv = l_run[r] > 0.f ? 1.f / l_run[r] : 0.f;
+      bf16* dst = p.out + (size_t)t * p.ldo + (size_t)hd * p.R + cg * NT16 * 16 + 2 * c4;
+#pragma unroll
+      for (int i = 0; i < 2 * NT16; ++i)
+        *reinterpret_cast<uint32_t*>(dst + i * 8) = pack_bf16(o[i][2 * r] * inv, o[i][2 * r + 1] * inv);
+    } else {
+      const size_t row = (size_t)t * p.H + hd;
+      float* dst = p.part_o + (row * p.splits + blockIdx.z) * p.R + cg * NT16 * 16 + 2 * c4;
+#pragma unroll
+      for (int i = 0; i < 2 * NT16; ++i) *reinterpret_cast<float2*>(dst + i * 8) = make_float2(o[i][2 * r], o[i][2 * r + 1]);
+      if (cg == 0 && c4 == 0) {
+        p.part_ml[(row * p.splits + blockIdx.z) * 2] = m_run[r];
+        p.part_ml[(row * p.splits + blockIdx.z) * 2 + 1] = l_run[r];
+      }
+    }
+  }
+}
+
+template <int NT16>
+int launch(const Args& a, int num_tiles, int head_chunks, cudaStream_t stream) {
+  const int ROWB = key_row_bytes(a.R + a.r);
+  const size_t smem = (size_t)BM * ROWB + 2 * (size_t)BN * ROWB + BM * P_ROWB + 2 * BM * 4 * sizeof(float);
+  if (smem > 227 * 1024) return 2;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attn_latent_mma_kernel<NT16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
+      return 4;
+    configured = true;
+  }
+  if (launch_pdl(attn_latent_mma_kernel<NT16>, dim3(num_tiles, head_chunks, a.splits), dim3(THREADS), smem, stream, a) != cudaSuccess)
+    return 1;
+  return 0;
+}
+}  // namespace tc
+
+// Tiles tile_offset .. tile_offset + num_tiles - 1 of the tile list (TPT tokens a tile).  splits > 1:
+// unnormalised partials go to part_o [rows, splits, R] and part_ml [rows, splits, 2], rows being
+// flat token * H + head.  Sizes: R a multiple of 64 up to 512 (not 320 or 448), r a multiple of 16,
+// row strides of qa in pairs of floats, pools and out in bfloat16.
+extern "C" int dsp_attn_latent_mma(const float* qa, long ldqa, const void* q, int q_dtype, long ldq,
+                                   int q_head_stride, int qr_off, const float* inv_freq, int rot,
+                                   const void* c_pool, const void* r_pool, const int* page_table,
+                                   int pt_stride, const int* q_start, const int* ctx_len,
+                                   const int* tile_seq, const int* tile_tok0, int tile_offset,
+                                   int num_tiles, void* out, long ldo, float* part_o, float* part_ml,
+                                   int splits, int H, int TPT, int R, int r, int page_size, int num_pages,
+                                   float scale, cudaStream_t stream) {
+  if (num_tiles == 0) return 0;
+  int* err = dsp_device_error_ptr();
+  DSP_REQUIRE(err != nullptr, "dsp_attn_latent_mma: no device error word");
+  DSP_REQUIRE(R % 64 == 0 && r % 16 == 0 && r >= 0 && rot % 2 == 0 && rot <= r, "dsp_attn_latent_mma: R=%d r=%d rot=%d", R, r, rot);
+  DSP_REQUIRE(ldqa % 2 == 0 && ((uintptr_t)qa % 8) == 0 && ldo % 2 == 0 && ((uintptr_t)out % 4) == 0 &&
+              ((uintptr_t)c_pool % 16) == 0 && ((uintptr_t)r_pool % 16) == 0, "dsp_attn_latent_mma: operand alignment");
+  DSP_REQUIRE(splits >= 1 && (splits == 1 || (part_o && part_ml)), "dsp_attn_latent_mma: splits=%d without scratch", splits);
+  const int HC = H < tc::BM ? H : tc::BM;
+  DSP_REQUIRE(TPT >= 1 && TPT * HC <= tc::BM, "dsp_attn_latent_mma: %d tokens x %d heads exceed a tile", TPT, HC);
+  tc::Args a;
+  a.qa = qa; a.ldqa = ldqa; a.q = q; a.q_dtype = q_dtype; a.ldq = ldq; a.q_head_stride = q_head_stride; a.qr_off = qr_off;
+  a.inv_freq = inv_freq; a.rot = rot; a.c_pool = (const bf16*)c_pool; a.r_pool = (const bf16*)r_pool;
+  a.page_table = page_table; a.pt_stride = pt_stride; a.q_start = q_start; a.ctx_len = ctx_len;
+  a.tile_seq = tile_seq; a.tile_tok0 = tile_tok0; a.tile_offset = tile_offset;
+  a.out = (bf16*)out; a.ldo = ldo; a.part_o = part_o; a.part_ml = part_ml; a.splits = splits;
+  a.H = H; a.HC = HC; a.TPT = TPT; a.R = R; a.r = r; a.page_size = page_size; a.num_pages = num_pages;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.err = err;
+  const int chunks = (H + HC - 1) / HC;
+  int rc;
+  switch (R / 64) {
+    case 1: rc = tc::launch<1>(a, num_tiles, chunks, stream); break;
+    case 2: rc = tc::launch<2>(a, num_tiles, chunks, stream); break;
+    case 3: rc = tc::launch<3>(a, num_tiles, chunks, stream); break;
+    case 4: rc = tc::launch<4>(a, num_tiles, chunks, stream); break;
+    case 6: rc = tc::launch<6>(a, num_tiles, chunks, stream); break;
+    case 8: rc = tc::launch<8>(a, num_tiles, chunks, stream); break;
+    default: DSP_REQUIRE(false, "dsp_attn_latent_mma: latent size %d is not built", R);
+  }
+  DSP_REQUIRE(rc == 0, "dsp_attn_latent_mma: launch failed (%d)", rc);
+  DSP_CHECK_LAUNCH("dsp_attn_latent_mma");
+  return 0;
+}

@@ -62,3 +62,70 @@ def latent_attention(q_absorbed: torch.Tensor, q: torch.Tensor, q_head_stride: i
         L.dtype_code(out_dtype), L.i64(out.stride(0)), T, num_heads, R, r, page_size, num_pages, L.f32(scale),
         L.stream_handle()))
     return out
+
+
+MMA_ROWS_PER_TILE = 64  # query rows, (token, head) pairs, of one tile of the tensor-core kernel
+MMA_KEYS_PER_TILE = 32
+_MMA_LATENT_SIZES = (64, 128, 192, 256, 384, 512)
+
+
+def mma_tokens_per_tile(num_heads: int) -> int:
+    """Query tokens of one request that share a tile of the tensor-core kernel."""
+    return max(1, MMA_ROWS_PER_TILE // min(num_heads, MMA_ROWS_PER_TILE))
+
+
+def mma_supported(kv_rank: int, rot_dim: int, pool_dtype: torch.dtype) -> bool:
+    row_bytes = ((2 * (kv_rank + rot_dim) + 127) // 128) * 128 + 16
+    return (pool_dtype == torch.bfloat16 and kv_rank in _MMA_LATENT_SIZES and rot_dim % 16 == 0
+            and 128 * row_bytes + 64 * 80 + 2048 <= 227 * 1024)
+
+
+def choose_key_splits(num_tiles: int, head_chunks: int, max_ctx: int, device) -> int:
+    """Key ranges per single-token tile so that the launch covers the device about once, each
+    range keeping at least four key tiles."""
+    from dispec_b200.ops import tuning
+    ctas = max(1, num_tiles * head_chunks)
+    want = max(1, tuning.sm_count(device) // ctas)
+    room = max(1, -(-max_ctx // MMA_KEYS_PER_TILE) // 4)
+    return int(min(want, room, tuning.MAX_SPLITS))
+
+
+def latent_attention_tiles(ctx, q_absorbed: torch.Tensor, q: torch.Tensor, q_head_stride: int, qr_off: int,
+                           inv_freq: torch.Tensor | None, rot: int, c_pool: torch.Tensor, r_pool: torch.Tensor,
+                           page_table: torch.Tensor, num_heads: int, scale: float) -> torch.Tensor:
+    """The same attention on tensor cores (bfloat16 pools), over the step's tile list for
+    ``mma_tokens_per_tile(num_heads)`` tokens a tile.  Single tokens (the first tiles) have their
+    keys cut into ranges that are merged by ``dsp_attn_combine``; portions of prompts run whole."""
+    from dispec_b200.ops import attention as attn_ops
+    num_pages, _, page_size, R = c_pool.shape
+    r = r_pool.shape[3]
+    T = q_absorbed.shape[0]
+    tpt = mma_tokens_per_tile(num_heads)
+    tile_seq, tile_tok0, n_tiles = ctx.attention_tiles[tpt]
+    assert q_absorbed.dtype == torch.float32 and q_absorbed.stride(1) == 1 and q.stride(1) == 1
+    assert c_pool.dtype == torch.bfloat16 and c_pool.is_contiguous() and r_pool.is_contiguous()
+    out = torch.empty((T, num_heads * R), dtype=torch.bfloat16, device=q.device)
+    lib = L.mixer_library("attn_latent")
+    chunks = -(-num_heads // MMA_ROWS_PER_TILE)
+
+    def launch(offset, count, splits, part_o, part_ml):
+        L.check(lib.dsp_attn_latent_mma(
+            L.ptr(q_absorbed), L.i64(q_absorbed.stride(0)), L.ptr(q), L.dtype_code(q.dtype), L.i64(q.stride(0)),
+            q_head_stride, qr_off, L.ptr(inv_freq), rot, L.ptr(c_pool), L.ptr(r_pool), L.ptr(page_table),
+            page_table.stride(0), L.ptr(ctx.q_start), L.ptr(ctx.ctx_len), L.ptr(tile_seq), L.ptr(tile_tok0), offset,
+            count, L.ptr(out), L.i64(out.stride(0)), L.ptr(part_o), L.ptr(part_ml), splits, num_heads, tpt, R, r,
+            page_size, num_pages, L.f32(scale), L.stream_handle()))
+
+    n_dec = ctx.num_decode_seqs  # single tokens come first, one tile each
+    if n_dec:
+        splits = choose_key_splits(n_dec, chunks, ctx.max_ctx_len, q.device)
+        if splits > 1:
+            part_o, part_ml = attn_ops._partial_buffers(q.device, n_dec * num_heads, splits, R)
+            launch(0, n_dec, splits, part_o, part_ml)
+            L.check(L.core().dsp_attn_combine(L.ptr(part_o), L.ptr(part_ml), L.ptr(out), L.i64(out.stride(0)),
+                                              n_dec, num_heads, R, splits, L.dtype_code(out.dtype), L.stream_handle()))
+        else:
+            launch(0, n_dec, 1, None, None)
+    if n_tiles > n_dec:
+        launch(n_dec, n_tiles - n_dec, 1, None, None)
+    return out

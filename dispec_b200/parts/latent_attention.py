@@ -61,6 +61,9 @@ class LatentAttention(Mixer):
     def cache_need(self):
         return CacheNeed((CacheTensor("latent", 1, self.kv_rank), CacheTensor("rotated_key", 1, self.rot_dim)), 0)
 
+    def tokens_per_attention_tile(self):
+        return latent_ops.mma_tokens_per_tile(self.num_heads)
+
     def forward(self, ctx, x, cache, state):
         H, d, r, dv, R, Q = self.num_heads, self.dim, self.rot_dim, self.vdim, self.kv_rank, self.q_rank
         T = x.shape[0]
@@ -79,8 +82,13 @@ class LatentAttention(Mixer):
         qa = torch.empty((T, H * R), dtype=torch.float32, device=x.device)
         for a in range(H):
             ops.linear(q[:, a * (d + r):a * (d + r) + d], self.w_uk_t[a], out=qa[:, a * R:(a + 1) * R])
-        mixed = latent_ops.latent_attention(qa, q, d + r, d, inv_freq, rot_n, c_pool, r_pool, cache.page_table,
-                                            ctx.positions, ctx.seq_of_token, H, scale, x.dtype)
+        if (latent_ops.mma_supported(R, r, c_pool.dtype)
+                and latent_ops.mma_tokens_per_tile(H) in ctx.attention_tiles):
+            mixed = latent_ops.latent_attention_tiles(ctx, qa, q, d + r, d, inv_freq, rot_n, c_pool, r_pool,
+                                                      cache.page_table, H, scale)
+        else:  # the 32-bit path, and sizes the tensor-core kernel is not built for
+            mixed = latent_ops.latent_attention(qa, q, d + r, d, inv_freq, rot_n, c_pool, r_pool, cache.page_table,
+                                                ctx.positions, ctx.seq_of_token, H, scale, x.dtype)
         heads = torch.empty((T, H * dv), dtype=x.dtype, device=x.device)
         for a in range(H):
             ops.linear(mixed[:, a * R:(a + 1) * R], self.w_uv[a], out=heads[:, a * dv:(a + 1) * dv])

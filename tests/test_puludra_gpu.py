@@ -329,3 +329,73 @@ def test_latent_store_kernel_norms_rotates_and_places():
         assert (r_pool[pg, 0, off].cpu().double() - k).abs().max() < 1e-5
         written += 1
     assert int(torch.isfinite(c_pool[:, 0, :, 0]).sum()) == written  # nothing else was touched
+
+
+@pytest.mark.parametrize("H,R,r,page", [(10, 192, 16, 16), (12, 512, 64, 16), (70, 64, 32, 8), (3, 128, 0, 32)])
+def test_latent_attention_on_tensor_cores_matches_the_plain_softmax(H, R, r, page):
+    """The tensor-core kernel over a step of two single tokens (keys cut into ranges and merged)
+    and a portion of a prompt whose tiles end in the middle of a key tile; every query is aimed at
+    one key: the first, both sides of a page border, its own position, or the next one (stored,
+    invisible).  Scattered pages, NaN everywhere else."""
+    from types import SimpleNamespace
+    from dispec_b200.ops import latent as LO
+    g = torch.Generator().manual_seed(H + R)
+    lens = [3 * page + 5, 200, 9 * page + 7]  # stored tokens per request; the third brings a portion
+    portion = 45
+    n_pages = sum(-(-n // page) for n in lens) + 3
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    tables, lat, rk = [], [], []
+    width = max(-(-n // page) for n in lens)
+    c_pool = torch.full((n_pages, 1, page, R), float("nan"))
+    r_pool = torch.full((n_pages, 1, page, max(r, 1)), float("nan"))[..., :r]
+    for n in lens:
+        need = -(-n // page)
+        tables.append([perm.pop() for _ in range(need)] + [-1] * (width - need))
+        lat.append(torch.randn(n, R, generator=g).bfloat16().float())
+        rk.append(torch.randn(n, r, generator=g).bfloat16().float())
+        for j in range(n):
+            c_pool[tables[-1][j // page], 0, j % page] = lat[-1][j]
+            r_pool[tables[-1][j // page], 0, j % page] = rk[-1][j]
+    q_lens = [1, 1, portion]
+    seq_of, pos = [], []
+    for s, (n, ql) in enumerate(zip(lens, q_lens)):
+        seq_of += [s] * ql
+        pos += list(range(n - ql, n))
+    T = len(pos)
+    aims = [0, page - 1, page, None, "self", "next"]
+    star = []
+    for t in range(T):
+        a = aims[t % len(aims)]
+        n = lens[seq_of[t]]
+        star.append(a if isinstance(a, int) else pos[t] if a == "self" else min(pos[t] + 1, n - 1) if a == "next" else pos[t] // 2)
+    rot = r
+    inv_freq = (50.0 ** (-torch.arange(0, max(rot, 2), 2).double() / max(rot, 1))).float()
+    qa = torch.randn(T, H, R, generator=g) * 0.05
+    q_rot = torch.randn(T, H, r, generator=g) * 0.05
+    for t in range(T):
+        c = lat[seq_of[t]][star[t]]
+        qa[t] += 8.0 * c / c.norm() ** 2 * math.sqrt(R)
+    qraw = torch.zeros(T, H * (8 + r))
+    for a in range(H):
+        qraw[:, a * (8 + r) + 8:(a + 1) * (8 + r)] = q_rot[:, a]
+    qraw = qraw.bfloat16()
+    tpt = LO.mma_tokens_per_tile(H)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda:0")
+    tiles = [(s, a) for s, ql in enumerate(q_lens) for a in range(0, ql, tpt)]
+    ctx = SimpleNamespace(attention_tiles={tpt: (i32([s for s, _ in tiles]), i32([a for _, a in tiles]), len(tiles))},
+                          q_start=i32([0, 1, 2, 2 + portion]), ctx_len=i32(lens), num_decode_seqs=2, max_ctx_len=max(lens))
+    assert LO.mma_supported(R, r, torch.bfloat16)
+    scale = 0.21
+    out = LO.latent_attention_tiles(ctx, dev(qa.reshape(T, -1)), dev(qraw, torch.bfloat16), 8 + r, 8, dev(inv_freq), rot,
+                                    dev(c_pool, torch.bfloat16), dev(r_pool, torch.bfloat16), i32(tables), H, scale)
+    out = out.float().cpu().double().view(T, H, R)
+    assert torch.isfinite(out).all()
+    for t in range(T):
+        s_, p = seq_of[t], pos[t]
+        qr = q_rot[t].bfloat16().double()
+        if rot:
+            qr = plain.rotate_interleaved(qr[None], torch.tensor([p]), 50.0, rot)[0]
+        sc = (qa[t].double() @ lat[s_][:p + 1].double().T + qr @ rk[s_][:p + 1].double().T) * scale
+        w = torch.softmax(sc, dim=-1)
+        want = w @ lat[s_][:p + 1].double()
+        assert (out[t] - want).abs().max() < 0.05 * max(1.0, want.abs().max().item()), (t, star[t], p)
