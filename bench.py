@@ -595,6 +595,7 @@ def puludra_points(args, pk: dict) -> dict:
                 out[f"{key}_decode_b{b}_ms"] = round(ms, 4)
                 out[f"{key}_decode_b{b}_hbm_frac"] = round(step_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
                 out[f"{key}_decode_b{b}_launches_per_step"] = launches // steps
+                print(f"bench: {key} decode at batch {b}: {ms:.3f} ms a step", file=sys.stderr, flush=True)
                 if b == 1:
                     pms = prefill_time(r, random_prompts(1, PREFILL_TOKENS, vocab, 12)[0], repeats=3)
                     out[f"{key}_prefill"] = round(PREFILL_TOKENS / pms * 1000.0, 1)

@@ -17,14 +17,18 @@
 // One block per (request, head, tile of value columns).  A thread holds ROWS state rows of one
 // column in registers; the SLICES threads that share a column sit in adjacent lanes and add
 // their partial outputs by shuffles.  Tokens are staged through shared memory in rounds of
-// `tokens_per_round`, transformed as they are staged.  A request whose first row carries a
-// negative position (a padding row of a captured step) is skipped: its state slot belongs to
-// someone else.
+// `tokens_per_round`.  The recurrence is sequential in the tokens of a request, so what can be
+// done ahead of it is: for portions of prompts a first, fully parallel kernel writes q_t, b_t
+// (and a_t) of every token as floats, and the recurrence kernel only streams them in with
+// cp.async, the next round arriving while the current one is computed; single tokens are
+// transformed as they are staged, in one kernel.  A request whose first row carries a negative
+// position (a padding row of a captured step) is skipped: its state slot belongs to someone else.
 #include "common.cuh"
 
 namespace {
 
 enum { FIXED_DECAY = 0, FORGET_GATE = 1 };
+constexpr int THREADS = 256;
 
 struct RecurrenceArgs {
   const void* proj;  // [T, ld]: raw projection rows
@@ -45,13 +49,68 @@ struct RecurrenceArgs {
   const int* positions;    // [T]
   float* out;              // [T, ldo]: o_t at columns head * vdim + j
   long ldo;
+  float* ready;          // [T, planes, H * dim] floats written by the first kernel (null: transform while staging)
   int slices;            // threads per column (a power of two, at most 32)
   int cols_per_block;    // threads / slices
   int tokens_per_round;
 };
 
+// q_t, b_t and a_t of element (token, head, i) from the raw projection row, in 32-bit.
+__device__ __forceinline__ void transform(const RecurrenceArgs& p, int token, int head, int i, float& qv,
+                                          float& bv, float& av) {
+  const size_t rowp = (size_t)token * p.ld;
+  const size_t qo = rowp + p.q_off + (size_t)head * p.dim, ko = rowp + p.k_off + (size_t)head * p.dim;
+  av = 0.f;
+  if (p.mode == FIXED_DECAY) {
+    qv = ld_any(p.proj, p.proj_dtype, qo + i);
+    bv = ld_any(p.proj, p.proj_dtype, ko + i);
+    if (i < p.rot) {
+      const int half = p.rot / 2;
+      const int f = i < half ? i : i - half;
+      const int other = i < half ? i + half : i - half;
+      float sn, cs;
+      sincosf((float)p.positions[token] * p.inv_freq[f], &sn, &cs);
+      const float q2 = ld_any(p.proj, p.proj_dtype, qo + other);
+      const float k2 = ld_any(p.proj, p.proj_dtype, ko + other);
+      // first of the pair: u cos - v sin; second: v cos + u sin
+      qv = i < half ? qv * cs - q2 * sn : qv * cs + q2 * sn;
+      bv = i < half ? bv * cs - k2 * sn : bv * cs + k2 * sn;
+    }
+    bv *= p.key_scale;
+  } else {
+    const float rq = ld_any(p.proj, p.proj_dtype, qo + i);
+    qv = rq / (1.f + expf(-rq));
+    const float rf = ld_any(p.proj, p.proj_dtype, ko + i) + p.gate_bias[head * p.dim + i];
+    const float lo = p.lower[head * p.dim + i];
+    av = lo + (1.f - lo) * (1.f / (1.f + expf(-rf)));
+    bv = 1.f - av;
+  }
+}
+
+// ready[t][0] = q, [1] = b, [2] = a (FORGET_GATE only), each [H * dim]
+__global__ void __launch_bounds__(256) recurrence_prepare_kernel(const RecurrenceArgs p, int T) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int hd = p.H * p.dim, planes = p.mode == FORGET_GATE ? 3 : 2;
+  const long n = (long)T * hd;
+  for (long idx = (long)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (long)gridDim.x * blockDim.x) {
+    const int t = (int)(idx / hd), c = (int)(idx % hd);
+    if (p.positions[t] < 0) continue;
+    float qv, bv, av;
+    transform(p, t, c / p.dim, c % p.dim, qv, bv, av);
+    float* dst = p.ready + (size_t)t * planes * hd + c;
+    dst[0] = qv;
+    dst[hd] = bv;
+    if (planes == 3) dst[2 * hd] = av;
+  }
+}
+
+__device__ __forceinline__ void cp_async4(float* smem, const float* gmem) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem));
+}
+
 template <int ROWS>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(THREADS)
 linear_recurrence_kernel(const RecurrenceArgs p) {
   extern __shared__ float smem[];
   pdl_launch_dependents();
@@ -65,11 +124,11 @@ linear_recurrence_kernel(const RecurrenceArgs p) {
   const bool col_ok = col < p.vdim;
   const int dpad = p.slices * ROWS;  // state rows covered by the threads of a column (>= dim)
   const int R = p.tokens_per_round, C = p.cols_per_block;
-  float* qs = smem;               // [R][dpad]
-  float* bs = qs + R * dpad;      // [R][dpad]
-  float* as = bs + R * dpad;      // [R][dpad]  (FORGET_GATE only)
-  float* vs = as + (p.mode == FORGET_GATE ? R * dpad : 0);  // [R][C]
-  float* os = vs + R * C;         // [R][C]
+  const bool gate = p.mode == FORGET_GATE;
+  const int planes = gate ? 3 : 2;
+  // one staging buffer: [planes][R][dpad] then v [R][C]; two of them when rounds arrive by cp.async
+  const int buf_floats = planes * R * dpad + R * C;
+  float* os = smem + (p.ready ? 2 : 1) * buf_floats;  // [R][C]
 
   float* sp = p.state + (((size_t)p.state_slot[seq] * p.H + head) * p.dim) * p.vdim;
   float S[ROWS];
@@ -78,76 +137,89 @@ linear_recurrence_kernel(const RecurrenceArgs p) {
     const int i = slice + p.slices * k;
     S[k] = (col_ok && i < p.dim) ? sp[(size_t)i * p.vdim + col] : 0.f;
   }
-  const float decay = p.mode == FIXED_DECAY ? p.decay[head] : 0.f;
-  const int half = p.rot / 2;
+  const float decay = gate ? 0.f : p.decay[head];
+  const int hd = p.H * p.dim;
 
-  for (int base = t0; base < t1; base += R) {
+  // rows beyond dim stay zero in every buffer: they are written here once and never again
+  if (dpad > p.dim)
+    for (int idx = tid; idx < (p.ready ? 2 : 1) * buf_floats; idx += THREADS) smem[idx] = 0.f;
+  __syncthreads();
+
+  auto stage_async = [&](int base, float* buf) {
     const int n = min(R, t1 - base);
-    __syncthreads();
-    // stage and transform the round's tokens
-    for (int idx = tid; idx < n * dpad; idx += blockDim.x) {
-      const int r = idx / dpad, i = idx % dpad;
-      const size_t rowp = (size_t)(base + r) * p.ld;
-      float qv = 0.f, bv = 0.f, av = 0.f;
-      if (i < p.dim) {
-        const size_t qo = rowp + p.q_off + (size_t)head * p.dim, ko = rowp + p.k_off + (size_t)head * p.dim;
-        if (p.mode == FIXED_DECAY) {
-          qv = ld_any(p.proj, p.proj_dtype, qo + i);
-          bv = ld_any(p.proj, p.proj_dtype, ko + i);
-          if (i < p.rot) {
-            const int f = i < half ? i : i - half;
-            const int other = i < half ? i + half : i - half;
-            float sn, cs;
-            sincosf((float)p.positions[base + r] * p.inv_freq[f], &sn, &cs);
-            const float q2 = ld_any(p.proj, p.proj_dtype, qo + other);
-            const float k2 = ld_any(p.proj, p.proj_dtype, ko + other);
-            // first of the pair: u cos - v sin; second: v cos + u sin
-            qv = i < half ? qv * cs - q2 * sn : qv * cs + q2 * sn;
-            bv = i < half ? bv * cs - k2 * sn : bv * cs + k2 * sn;
-          }
-          bv *= p.key_scale;
-        } else {
-          const float rq = ld_any(p.proj, p.proj_dtype, qo + i);
-          qv = rq / (1.f + expf(-rq));
-          const float rf = ld_any(p.proj, p.proj_dtype, ko + i) + p.gate_bias[head * p.dim + i];
-          const float lo = p.lower[head * p.dim + i];
-          av = lo + (1.f - lo) * (1.f / (1.f + expf(-rf)));
-          bv = 1.f - av;
-        }
-      }
-      qs[idx] = qv;
-      bs[idx] = bv;
-      if (p.mode == FORGET_GATE) as[idx] = av;
+    for (int idx = tid; idx < planes * n * p.dim; idx += THREADS) {
+      const int pl = idx / (n * p.dim), rem = idx % (n * p.dim), r = rem / p.dim, i = rem % p.dim;
+      cp_async4(buf + (pl * R + r) * dpad + i, p.ready + ((size_t)(base + r) * planes + pl) * hd + head * p.dim + i);
     }
-    for (int idx = tid; idx < n * C; idx += blockDim.x) {
+    asm volatile("cp.async.commit_group;\n");
+  };
+  auto stage_values = [&](int base, float* buf) {
+    const int n = min(R, t1 - base);
+    float* vs = buf + planes * R * dpad;
+    for (int idx = tid; idx < n * C; idx += THREADS) {
       const int r = idx / C, c = blockIdx.x * C + idx % C;
       vs[idx] = c < p.vdim ? ld_any(p.proj, p.proj_dtype, (size_t)(base + r) * p.ld + p.v_off + (size_t)head * p.vdim + c) : 0.f;
+    }
+  };
+
+  if (p.ready) stage_async(t0, smem);
+  int turn = 0;
+  for (int base = t0; base < t1; base += R, turn ^= 1) {
+    const int n = min(R, t1 - base);
+    float* buf = smem + (p.ready ? turn : 0) * buf_floats;
+    float* qs = buf;
+    float* bs = buf + R * dpad;
+    float* as = buf + 2 * R * dpad;
+    float* vs = buf + planes * R * dpad;
+    if (p.ready) {
+      stage_values(base, buf);
+      if (base + R < t1) {
+        stage_async(base + R, smem + (turn ^ 1) * buf_floats);
+        asm volatile("cp.async.wait_group 1;\n");
+      } else {
+        asm volatile("cp.async.wait_group 0;\n");
+      }
+    } else {
+      for (int idx = tid; idx < n * p.dim; idx += THREADS) {
+        const int r = idx / p.dim, i = idx % p.dim;
+        float qv, bv, av;
+        transform(p, base + r, head, i, qv, bv, av);
+        qs[r * dpad + i] = qv;
+        bs[r * dpad + i] = bv;
+        if (gate) as[r * dpad + i] = av;
+      }
+      stage_values(base, buf);
     }
     __syncthreads();
     for (int r = 0; r < n; ++r) {
       const float v = vs[r * C + col_local];
       const float* qr = qs + r * dpad + slice;
       const float* br = bs + r * dpad + slice;
-      float acc = 0.f;
-      if (p.mode == FORGET_GATE) {
+      float acc0 = 0.f, acc1 = 0.f;
+      if (gate) {
         const float* ar = as + r * dpad + slice;
 #pragma unroll
-        for (int k = 0; k < ROWS; ++k) {
+        for (int k = 0; k < ROWS; k += 2) {
           S[k] = fmaf(ar[p.slices * k], S[k], br[p.slices * k] * v);
-          acc = fmaf(S[k], qr[p.slices * k], acc);
+          acc0 = fmaf(S[k], qr[p.slices * k], acc0);
+          S[k + 1] = fmaf(ar[p.slices * (k + 1)], S[k + 1], br[p.slices * (k + 1)] * v);
+          acc1 = fmaf(S[k + 1], qr[p.slices * (k + 1)], acc1);
         }
       } else {
 #pragma unroll
-        for (int k = 0; k < ROWS; ++k) {
+        for (int k = 0; k < ROWS; k += 2) {
           S[k] = fmaf(decay, S[k], br[p.slices * k] * v);
-          acc = fmaf(S[k], qr[p.slices * k], acc);
+          acc0 = fmaf(S[k], qr[p.slices * k], acc0);
+          S[k + 1] = fmaf(decay, S[k + 1], br[p.slices * (k + 1)] * v);
+          acc1 = fmaf(S[k + 1], qr[p.slices * (k + 1)], acc1);
         }
       }
+      float acc = acc0 + acc1;
       for (int o = 1; o < p.slices; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
       if (slice == 0) os[r * C + col_local] = acc;
     }
     __syncthreads();
-    for (int idx = tid; idx < n * C; idx += blockDim.x) {
+    for (int idx = tid; idx < n * C; idx += THREADS) {
       const int r = idx / C, c = blockIdx.x * C + idx % C;
       if (c < p.vdim) p.out[(size_t)(base + r) * p.ldo + (size_t)head * p.vdim + c] = os[idx];
     }
@@ -167,19 +239,26 @@ int launch(const RecurrenceArgs& a, int S, size_t smem, cudaStream_t stream) {
     configured = smem;
   }
   dim3 grid((a.vdim + a.cols_per_block - 1) / a.cols_per_block, a.H, S);
-  DSP_CUDA(launch_pdl(linear_recurrence_kernel<ROWS>, grid, dim3(128), smem, stream, a));
+  linear_recurrence_kernel<ROWS><<<grid, THREADS, smem, stream>>>(a);
   DSP_CHECK_LAUNCH("dsp_linear_recurrence");
   return 0;
 }
 }  // namespace
 
+// Floats of scratch the two-kernel form needs for T tokens (0: mode unknown).
+extern "C" long dsp_linear_recurrence_scratch(int mode, int H, int dim, long T) {
+  return (long)(mode == FORGET_GATE ? 3 : 2) * H * dim * T;
+}
+
+// scratch: null (one kernel, tokens transformed as they are staged) or room for
+// dsp_linear_recurrence_scratch floats (a first kernel transforms every token, the recurrence streams).
 extern "C" int dsp_linear_recurrence(const void* proj, int proj_dtype, long ld, int q_off, int k_off,
                                      int v_off, int mode, int H, int dim, int vdim, const float* decay,
                                      const float* inv_freq, int rot, float key_scale,
                                      const float* gate_bias, const float* lower, float* state,
                                      const int* state_slot, const int* q_start, const int* positions,
-                                     float* out, long ldo, int S, cudaStream_t stream) {
-  if (S == 0) return 0;
+                                     float* out, long ldo, int S, int T, float* scratch, cudaStream_t stream) {
+  if (S == 0 || T == 0) return 0;
   DSP_REQUIRE(proj && state && state_slot && q_start && positions && out, "dsp_linear_recurrence: missing operand");
   DSP_REQUIRE(H > 0 && H <= 65535 && S <= 65535, "dsp_linear_recurrence: H=%d, S=%d outside the grid", H, S);
   DSP_REQUIRE(dim > 0 && dim <= 1024 && vdim > 0, "dsp_linear_recurrence: dim=%d (at most 1024), vdim=%d", dim, vdim);
@@ -198,18 +277,27 @@ extern "C" int dsp_linear_recurrence(const void* proj, int proj_dtype, long ld, 
   a.decay = decay; a.inv_freq = inv_freq; a.rot = rot; a.key_scale = key_scale;
   a.gate_bias = gate_bias; a.lower = lower;
   a.state = state; a.state_slot = state_slot; a.q_start = q_start; a.positions = positions;
-  a.out = out; a.ldo = ldo;
-  // threads per column: four, or as many as keep a thread's rows at 32 (a power of two)
-  int slices = 4;
-  while ((dim + slices - 1) / slices > 32) slices *= 2;
+  a.out = out; a.ldo = ldo; a.ready = scratch;
+  // threads per column: as many as bring a thread's state rows down to 8 (a power of two, at
+  // most a warp); beyond 256 rows a thread holds 16 or 32
+  int slices = 1;
+  while (slices < 32 && (dim + slices - 1) / slices > 8) slices *= 2;
   const int rows = (dim + slices - 1) / slices;
   a.slices = slices;
-  a.cols_per_block = 128 / slices;
+  a.cols_per_block = THREADS / slices;
   const int R = rows <= 8 ? 8 : (rows <= 16 ? 16 : 32);
   const int dpad = slices * R;
-  a.tokens_per_round = dpad <= 128 ? 16 : 8;
-  const size_t smem = sizeof(float) * ((size_t)a.tokens_per_round * dpad * (mode == FORGET_GATE ? 3 : 2) +
-                                       (size_t)a.tokens_per_round * a.cols_per_block * 2);
+  a.tokens_per_round = dpad <= 256 ? 16 : 8;
+  const int planes = mode == FORGET_GATE ? 3 : 2;
+  const size_t buf = (size_t)planes * a.tokens_per_round * dpad + (size_t)a.tokens_per_round * a.cols_per_block;
+  const size_t smem = sizeof(float) * ((scratch ? 2 : 1) * buf + (size_t)a.tokens_per_round * a.cols_per_block);
+  if (scratch) {
+    const long n = (long)T * H * dim;
+    const int sms = dsp_num_sms();
+    const long want = (n + 255) / 256, cap = (long)(sms > 0 ? sms : 148) * 8;
+    recurrence_prepare_kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, stream>>>(a, T);
+    DSP_CHECK_LAUNCH("dsp_linear_recurrence (first kernel)");
+  }
   if (R == 8) return launch<8>(a, S, smem, stream);
   if (R == 16) return launch<16>(a, S, smem, stream);
   return launch<32>(a, S, smem, stream);

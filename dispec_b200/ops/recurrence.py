@@ -29,11 +29,18 @@ def linear_recurrence(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, mo
         assert t is None or (t.dtype == torch.float32 and t.is_contiguous() and t.is_cuda)
     S = state_slot.shape[0]
     assert q_start.shape[0] == S + 1
-    out = torch.empty((proj.shape[0], num_heads * vdim), dtype=torch.float32, device=proj.device)
+    T = proj.shape[0]
+    out = torch.empty((T, num_heads * vdim), dtype=torch.float32, device=proj.device)
     lib = L.mixer_library("linear_recurrence")
+    # portions of prompts: a first, parallel kernel writes q_t, b_t (a_t) of every token as floats and
+    # the sequential kernel streams them; steps of (nearly) single tokens transform while staging
+    scratch = None
+    if T > 2 * S:
+        planes = 3 if mode == FORGET_GATE else 2
+        scratch = torch.empty((T, planes, num_heads * dim), dtype=torch.float32, device=proj.device)
     L.check(lib.dsp_linear_recurrence(
         L.ptr(proj), L.dtype_code(proj.dtype), L.i64(proj.stride(0)), q_off, k_off, v_off, mode, num_heads, dim,
         vdim, L.ptr(decay), L.ptr(inv_freq), rot, L.f32(key_scale), L.ptr(gate_bias), L.ptr(lower), L.ptr(state),
-        L.ptr(state_slot), L.ptr(q_start), L.ptr(positions), L.ptr(out), L.i64(out.stride(0)), S,
-        L.stream_handle()))
+        L.ptr(state_slot), L.ptr(q_start), L.ptr(positions), L.ptr(out), L.i64(out.stride(0)), S, T,
+        L.ptr(scratch), L.stream_handle()))
     return out
