@@ -32,8 +32,6 @@ latent_store_kernel(const void* __restrict__ down, int d_dtype, long ldd, int c_
                     void* __restrict__ r_pool, int pool_dtype, int R, int r, int page_size,
                     int num_pages, int* err) {
   __shared__ float scratch[32];
-  pdl_launch_dependents();
-  pdl_wait();
   const int t = blockIdx.x;
   const int pos = positions[t];
   if (pos < 0) return;
@@ -80,8 +78,6 @@ attn_latent_kernel(const float* __restrict__ qa, long ldqa, const void* __restri
   float* ps = qs + GCHUNK * W;             // [GCHUNK][THREADS]
   long* place = (long*)(ps + GCHUNK * THREADS);  // [THREADS] row of each key in the pools
   __shared__ float red[GCHUNK][THREADS / 32];
-  pdl_launch_dependents();
-  pdl_wait();
   const int t = blockIdx.x, h0 = blockIdx.y * GCHUNK;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int pos = positions[t];
@@ -225,7 +221,7 @@ int launch_attn(const float* qa, long ldqa, const void* q, int q_dtype, long ldq
     configured = smem;
   }
   dim3 grid(T_, (H + GCHUNK - 1) / GCHUNK);
-  DSP_CUDA(launch_pdl(attn_latent_kernel<T, DPT>, grid, dim3(THREADS), smem, stream, qa, ldqa, q, q_dtype,
+  DSP_CUDA(launch_plain(attn_latent_kernel<T, DPT>, grid, dim3(THREADS), smem, stream, qa, ldqa, q, q_dtype,
                       ldq, q_head_stride, qr_off, inv_freq, rot, (const T*)c_pool, (const T*)r_pool,
                       page_table, pt_stride, positions, seq_of_token, out, out_dtype, ldo, H, R, r,
                       page_size, num_pages, scale, err));
@@ -244,7 +240,7 @@ extern "C" int dsp_latent_store(const void* down, int d_dtype, long ldd, int c_o
   DSP_REQUIRE(err != nullptr, "dsp_latent_store: no device error word");
   DSP_REQUIRE(down && gain && c_pool && r_pool && R > 0 && r >= 0, "dsp_latent_store: missing operand");
   DSP_REQUIRE(rot >= 0 && rot <= r && rot % 2 == 0 && (rot == 0 || inv_freq), "dsp_latent_store: rot=%d of %d", rot, r);
-  DSP_CUDA(launch_pdl(latent_store_kernel, dim3(T_), dim3(THREADS), 0, stream, down, d_dtype, ldd, c_off,
+  DSP_CUDA(launch_plain(latent_store_kernel, dim3(T_), dim3(THREADS), 0, stream, down, d_dtype, ldd, c_off,
                       r_off, gain, eps, inv_freq, rot, positions, seq_of_token, page_table, pt_stride,
                       c_pool, r_pool, pool_dtype, R, r, page_size, num_pages, err));
   DSP_CHECK_LAUNCH("dsp_latent_store");
@@ -357,8 +353,6 @@ __global__ void __launch_bounds__(THREADS, 1) attn_latent_mma_kernel(const Args 
   const uint32_t p_s = k_s + 2 * BN * ROWB;
   float* red_max = reinterpret_cast<float*>(smem + (size_t)BM * ROWB + 2 * (size_t)BN * ROWB + BM * P_ROWB);  // [BM][4]
   float* red_sum = red_max + BM * 4;                                                                          // [BM][4]
-  pdl_launch_dependents();
-  pdl_wait();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int rg = warp & 3, cg = warp >> 2;
   const int tile = blockIdx.x + p.tile_offset;
@@ -561,7 +555,7 @@ int launch(const Args& a, int num_tiles, int head_chunks, cudaStream_t stream) {
       return 4;
     configured = true;
   }
-  if (launch_pdl(attn_latent_mma_kernel<NT16>, dim3(num_tiles, head_chunks, a.splits), dim3(THREADS), smem, stream, a) != cudaSuccess)
+  if (launch_plain(attn_latent_mma_kernel<NT16>, dim3(num_tiles, head_chunks, a.splits), dim3(THREADS), smem, stream, a) != cudaSuccess)
     return 1;
   return 0;
 }

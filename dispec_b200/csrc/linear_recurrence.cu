@@ -89,8 +89,6 @@ __device__ __forceinline__ void transform(const RecurrenceArgs& p, int token, in
 
 // ready[t][0] = q, [1] = b, [2] = a (FORGET_GATE only), each [H * dim]
 __global__ void __launch_bounds__(256) recurrence_prepare_kernel(const RecurrenceArgs p, int T) {
-  pdl_launch_dependents();
-  pdl_wait();
   const int hd = p.H * p.dim, planes = p.mode == FORGET_GATE ? 3 : 2;
   const long n = (long)T * hd;
   for (long idx = (long)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (long)gridDim.x * blockDim.x) {
@@ -113,8 +111,6 @@ template <int ROWS>
 __global__ void __launch_bounds__(THREADS)
 linear_recurrence_kernel(const RecurrenceArgs p) {
   extern __shared__ float smem[];
-  pdl_launch_dependents();
-  pdl_wait();
   const int seq = blockIdx.z, head = blockIdx.y;
   const int t0 = p.q_start[seq], t1 = p.q_start[seq + 1];
   if (t1 <= t0 || p.positions[t0] < 0) return;

@@ -16,8 +16,6 @@ sum_norm_kernel(const void* __restrict__ x, int x_dtype, long ldx, const void* _
                 int y_dtype, long ld16, int width) {
   extern __shared__ float row[];
   __shared__ float scratch[32];
-  pdl_launch_dependents();
-  pdl_wait();
   const int r = blockIdx.x;
   const size_t in_row = rows ? (size_t)rows[r] : (size_t)r;
   float ss = 0.f;
@@ -42,8 +40,6 @@ __global__ void __launch_bounds__(128)
 head_norm_gate_kernel(const float* __restrict__ o, long ldo, const float* __restrict__ gain,
                       const void* __restrict__ gate, int g_dtype, long ldg, void* __restrict__ y,
                       int y_dtype, long ldy, int T, int H, int dv, float eps) {
-  pdl_launch_dependents();
-  pdl_wait();
   const int lane = threadIdx.x & 31;
   const long pair = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (pair >= (long)T * H) return;
@@ -72,8 +68,6 @@ __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log
 __global__ void __launch_bounds__(256)
 xielu_kernel(const void* __restrict__ z, int z_dtype, long ldz, const float* __restrict__ pq,
              void* __restrict__ y, int y_dtype, long ldy, long rows, int cols) {
-  pdl_launch_dependents();
-  pdl_wait();
   const float ap = softplus_f(pq[0]), an = 0.5f + softplus_f(pq[1]);
   const long n = rows * cols;
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
@@ -99,7 +93,7 @@ extern "C" int dsp_sum_norm(const void* x, int x_dtype, long ldx, const void* de
     DSP_CUDA(cudaFuncSetAttribute(sum_norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = smem;
   }
-  DSP_CUDA(launch_pdl(sum_norm_kernel, dim3(n_rows), dim3(256), smem, stream, x, x_dtype, ldx, delta,
+  DSP_CUDA(launch_plain(sum_norm_kernel, dim3(n_rows), dim3(256), smem, stream, x, x_dtype, ldx, delta,
                       d_dtype, ldd, w, alpha, eps, rows, y32, ld32, y16, y_dtype, ld16, width));
   DSP_CHECK_LAUNCH("dsp_sum_norm");
   return 0;
@@ -111,7 +105,7 @@ extern "C" int dsp_head_norm_gate(const float* o, long ldo, const float* gain, c
   if (T == 0) return 0;
   DSP_REQUIRE(o && y && H > 0 && dv > 0, "dsp_head_norm_gate: missing operand");
   const long pairs = (long)T * H;
-  DSP_CUDA(launch_pdl(head_norm_gate_kernel, dim3((unsigned)((pairs + 3) / 4)), dim3(128), 0, stream, o,
+  DSP_CUDA(launch_plain(head_norm_gate_kernel, dim3((unsigned)((pairs + 3) / 4)), dim3(128), 0, stream, o,
                       ldo, gain, gate, g_dtype, ldg, y, y_dtype, ldy, T, H, dv, eps));
   DSP_CHECK_LAUNCH("dsp_head_norm_gate");
   return 0;
@@ -124,7 +118,7 @@ extern "C" int dsp_xielu(const void* z, int z_dtype, long ldz, const float* pq, 
   const long n = rows * cols;
   const int sms = dsp_num_sms();
   const long want = (n + 255) / 256, cap = (long)(sms > 0 ? sms : 148) * 16;
-  DSP_CUDA(launch_pdl(xielu_kernel, dim3((unsigned)(want < cap ? want : cap)), dim3(256), 0, stream, z,
+  DSP_CUDA(launch_plain(xielu_kernel, dim3((unsigned)(want < cap ? want : cap)), dim3(256), 0, stream, z,
                       z_dtype, ldz, pq, y, y_dtype, ldy, rows, cols));
   DSP_CHECK_LAUNCH("dsp_xielu");
   return 0;

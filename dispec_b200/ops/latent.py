@@ -3,6 +3,8 @@ normalised latent and rotated key part into the pages, and the attention itself 
 See ``csrc/attn_latent.cu``."""
 from __future__ import annotations
 
+import os
+
 import torch
 
 from dispec_b200.ops import library as L
@@ -75,6 +77,8 @@ def mma_tokens_per_tile(num_heads: int) -> int:
 
 
 def mma_supported(kv_rank: int, rot_dim: int, pool_dtype: torch.dtype) -> bool:
+    if os.environ.get("DISPEC_B200_LATENT_MMA") == "0":  # measurements: everything on the 32-bit kernel
+        return False
     row_bytes = ((2 * (kv_rank + rot_dim) + 127) // 128) * 128 + 16
     return (pool_dtype == torch.bfloat16 and kv_rank in _MMA_LATENT_SIZES and rot_dim % 16 == 0
             and 128 * row_bytes + 64 * 80 + 2048 <= 227 * 1024)
