@@ -606,3 +606,106 @@ extern "C" int dsp_attn_latent_mma(const float* qa, long ldqa, const void* q, in
   DSP_CHECK_LAUNCH("dsp_attn_latent_mma");
   return 0;
 }
+
+// ------------------------------------------------------ the per-head products around the attention
+// C_h = A_h W_h^T for every head h in one launch (bfloat16 operands, 32-bit accumulation):
+// folding the key map into the queries (A_h: the head's unrotated query part, W_h = Wk_h^T) and
+// applying the value map to the attention's result (A_h: sum_j p_j c_j, W_h = Wv_h).  A_h and C_h
+// are column blocks of row-major matrices (row strides lda / ldc, head strides a_hs / c_hs);
+// W is [H, N, K] contiguous.  64 x 64 tiles, k in steps of 32, cp.async in two buffers, mma.sync.
+namespace hp {
+constexpr int BM = 64, BN = 64, BK = 32, THREADS = 128, ROWB = 80;
+
+struct Args {
+  const bf16* A; long lda, a_hs;
+  const bf16* W;
+  void* C; int c_dtype; long ldc, c_hs;
+  int M, N, K;
+};
+
+__global__ void __launch_bounds__(THREADS) head_products_kernel(const Args p) {
+  __shared__ __align__(128) unsigned char sm[2][2][BM * ROWB];
+  const int z = blockIdx.z, m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const bf16* A = p.A + (size_t)z * p.a_hs;
+  const bf16* W = p.W + (size_t)z * p.N * p.K;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, wm = warp & 1, wn = warp >> 1;
+  const int g = lane >> 2, c4 = lane & 3, m8 = lane >> 3, l8 = lane & 7;
+  auto load = [&](int kb, int buf) {
+#pragma unroll
+    for (int c = tid; c < BM * 4; c += THREADS) {
+      const int row = c >> 2, ch = c & 3;
+      const bool va = m0 + row < p.M, vw = n0 + row < p.N;
+      const bf16* sa = va ? A + (size_t)(m0 + row) * p.lda + kb * BK + ch * 8 : A;
+      const bf16* sw = vw ? W + (size_t)(n0 + row) * p.K + kb * BK + ch * 8 : W;
+      tc::cp_async16((uint32_t)__cvta_generic_to_shared(&sm[buf][0][row * ROWB + ch * 16]), sa, va);
+      tc::cp_async16((uint32_t)__cvta_generic_to_shared(&sm[buf][1][row * ROWB + ch * 16]), sw, vw);
+    }
+    tc::cp_async_commit();
+  };
+  float acc[2][4][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.f;
+  const int nk = p.K / BK;
+  load(0, 0);
+  for (int kb = 0; kb < nk; ++kb) {
+    const int buf = kb & 1;
+    if (kb + 1 < nk) {
+      load(kb + 1, buf ^ 1);
+      tc::cp_async_wait<1>();
+    } else {
+      tc::cp_async_wait<0>();
+    }
+    __syncthreads();
+    const uint32_t as = (uint32_t)__cvta_generic_to_shared(&sm[buf][0][0]);
+    const uint32_t ws = (uint32_t)__cvta_generic_to_shared(&sm[buf][1][0]);
+#pragma unroll
+    for (int kk = 0; kk < BK / 16; ++kk) {
+      uint32_t a[2][4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+        tc::ldmatrix_x4(a[i], as + (wm * 32 + i * 16 + (m8 & 1) * 8 + l8) * ROWB + (kk * 2 + (m8 >> 1)) * 16);
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        uint32_t b[4];
+        tc::ldmatrix_x4(b, ws + (wn * 32 + j * 16 + (m8 >> 1) * 8 + l8) * ROWB + (kk * 2 + (m8 & 1)) * 16);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          tc::mma_bf16(acc[i][2 * j], a[i], b[0], b[1]);
+          tc::mma_bf16(acc[i][2 * j + 1], a[i], b[2], b[3]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int row = m0 + wm * 32 + i * 16 + g + (e >> 1) * 8;
+        const int col = n0 + wn * 32 + j * 8 + 2 * c4 + (e & 1);
+        if (row < p.M && col < p.N) st_any(p.C, p.c_dtype, (size_t)row * p.ldc + (size_t)z * p.c_hs + col, acc[i][j][e]);
+      }
+}
+}  // namespace hp
+
+extern "C" int dsp_head_products(const void* A, long lda, long a_hs, const void* W, void* C, int c_dtype,
+                                 long ldc, long c_hs, int M, int N, int K, int H, cudaStream_t stream) {
+  if (M == 0 || N == 0 || H == 0) return 0;
+  DSP_REQUIRE(A && W && C && K > 0 && K % hp::BK == 0, "dsp_head_products: K=%d must be a positive multiple of %d", K, hp::BK);
+  DSP_REQUIRE(lda % 8 == 0 && a_hs % 8 == 0 && ((uintptr_t)A % 16) == 0 && ((uintptr_t)W % 16) == 0 && ((long)N * K) % 8 == 0,
+              "dsp_head_products: operands must lie on 16-byte pieces");
+  DSP_REQUIRE(H <= 65535 && (M + hp::BM - 1) / hp::BM <= 65535, "dsp_head_products: grid too large");
+  hp::Args a;
+  a.A = (const bf16*)A; a.lda = lda; a.a_hs = a_hs; a.W = (const bf16*)W;
+  a.C = C; a.c_dtype = c_dtype; a.ldc = ldc; a.c_hs = c_hs; a.M = M; a.N = N; a.K = K;
+  DSP_CUDA(launch_plain(hp::head_products_kernel, dim3((N + hp::BN - 1) / hp::BN, (M + hp::BM - 1) / hp::BM, H),
+                        dim3(hp::THREADS), 0, stream, a));
+  DSP_CHECK_LAUNCH("dsp_head_products");
+  return 0;
+}

@@ -133,3 +133,24 @@ def latent_attention_tiles(ctx, q_absorbed: torch.Tensor, q: torch.Tensor, q_hea
     if n_tiles > n_dec:
         launch(n_dec, n_tiles - n_dec, 1, None, None)
     return out
+
+
+def head_products_supported(x: torch.Tensor, head_stride: int, w: torch.Tensor) -> bool:
+    """Whether ``head_products`` takes these operands: bfloat16, k in whole steps of 32, every
+    head's block of x on 16-byte pieces."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[2] % 32 == 0
+            and x.stride(1) == 1 and x.stride(0) % 8 == 0 and head_stride % 8 == 0 and x.data_ptr() % 16 == 0
+            and (w.shape[1] * w.shape[2]) % 8 == 0 and w.is_contiguous())
+
+
+def head_products(x: torch.Tensor, head_stride: int, w: torch.Tensor, out: torch.Tensor, out_head_stride: int) -> torch.Tensor:
+    """out[:, h * out_head_stride : + N] = x[:, h * head_stride : + K] @ w[h].T for every head h of
+    ``w`` [H, N, K] in one launch (bfloat16 operands, 32-bit accumulation; ``out`` float32 or
+    bfloat16, any column offset baked into the tensors handed in)."""
+    assert head_products_supported(x, head_stride, w) and out.stride(1) == 1 and out.is_cuda
+    H, N, K = w.shape
+    lib = L.mixer_library("attn_latent")
+    L.check(lib.dsp_head_products(L.ptr(x), L.i64(x.stride(0)), L.i64(head_stride), L.ptr(w), L.ptr(out),
+                                  L.dtype_code(out.dtype), L.i64(out.stride(0)), L.i64(out_head_stride), x.shape[0],
+                                  N, K, H, L.stream_handle()))
+    return out

@@ -55,7 +55,7 @@ class LatentAttention(Mixer):
         # the key map of head h as the matrix of the product that folds it into the query:
         # qa_h = q_plain_h W_uk_h, i.e. x W^T with W = W_uk_h^T [R, d]
         self.w_uk_t = tensors["uk.weight"].view(H, d, R).transpose(1, 2).contiguous()
-        self.w_uv = tensors["uv.weight"].view(H, self.vdim, R)
+        self.w_uv = tensors["uv.weight"].view(H, self.vdim, R).contiguous()
         self.w_o = tensors["o.weight"]
 
     def cache_need(self):
@@ -80,8 +80,11 @@ class LatentAttention(Mixer):
         cq = norm32_ops.sum_norm(down[:, :Q], self.q_gain, self.eps, out_dtype=x.dtype, want32=False)[1]
         q = ops.linear(cq, self.w_uq)  # [T, H * (d + r)]
         qa = torch.empty((T, H * R), dtype=torch.float32, device=x.device)
-        for a in range(H):
-            ops.linear(q[:, a * (d + r):a * (d + r) + d], self.w_uk_t[a], out=qa[:, a * R:(a + 1) * R])
+        if latent_ops.head_products_supported(q, d + r, self.w_uk_t):
+            latent_ops.head_products(q, d + r, self.w_uk_t, qa, R)
+        else:
+            for a in range(H):
+                ops.linear(q[:, a * (d + r):a * (d + r) + d], self.w_uk_t[a], out=qa[:, a * R:(a + 1) * R])
         if (latent_ops.mma_supported(R, r, c_pool.dtype)
                 and latent_ops.mma_tokens_per_tile(H) in ctx.attention_tiles):
             mixed = latent_ops.latent_attention_tiles(ctx, qa, q, d + r, d, inv_freq, rot_n, c_pool, r_pool,
@@ -90,6 +93,9 @@ class LatentAttention(Mixer):
             mixed = latent_ops.latent_attention(qa, q, d + r, d, inv_freq, rot_n, c_pool, r_pool, cache.page_table,
                                                 ctx.positions, ctx.seq_of_token, H, scale, x.dtype)
         heads = torch.empty((T, H * dv), dtype=x.dtype, device=x.device)
-        for a in range(H):
-            ops.linear(mixed[:, a * R:(a + 1) * R], self.w_uv[a], out=heads[:, a * dv:(a + 1) * dv])
+        if latent_ops.head_products_supported(mixed, R, self.w_uv):
+            latent_ops.head_products(mixed, R, self.w_uv, heads, dv)
+        else:
+            for a in range(H):
+                ops.linear(mixed[:, a * R:(a + 1) * R], self.w_uv[a], out=heads[:, a * dv:(a + 1) * dv])
         return ops.linear(heads, self.w_o, out_dtype=torch.float32)

@@ -399,3 +399,23 @@ def test_latent_attention_on_tensor_cores_matches_the_plain_softmax(H, R, r, pag
         w = torch.softmax(sc, dim=-1)
         want = w @ lat[s_][:p + 1].double()
         assert (out[t] - want).abs().max() < 0.05 * max(1.0, want.abs().max().item()), (t, star[t], p)
+
+
+@pytest.mark.parametrize("M,H,N,K,out_dtype", [(5, 3, 40, 32, torch.float32), (200, 12, 128, 512, torch.bfloat16),
+                                               (130, 2, 192, 64, torch.float32)])
+def test_head_products_kernel(M, H, N, K, out_dtype):
+    from dispec_b200.ops import latent as LO
+    g = torch.Generator().manual_seed(M)
+    pad = 8  # columns between the heads' blocks of x that the product must not read
+    x = torch.randn(M, H * (K + pad), generator=g).bfloat16()
+    w = (torch.randn(H, N, K, generator=g) / K ** 0.5).bfloat16()
+    out = torch.full((M, H * N + 3), float("nan"), dtype=out_dtype, device="cuda:0")
+    xd, wd = x.cuda(), w.cuda()
+    assert LO.head_products_supported(xd, K + pad, wd)
+    LO.head_products(xd, K + pad, wd, out, N)
+    for a in range(H):
+        want = x[:, a * (K + pad):a * (K + pad) + K].double() @ w[a].double().T
+        got = out[:, a * N:(a + 1) * N].double().cpu()
+        tol = 1e-4 if out_dtype == torch.float32 else 0.02
+        assert (got - want).abs().max() < tol * max(1.0, want.abs().max().item()), a
+    assert torch.isnan(out[:, H * N:]).all()
