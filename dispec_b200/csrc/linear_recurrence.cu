@@ -107,7 +107,12 @@ __device__ __forceinline__ void cp_async4(float* smem, const float* gmem) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem));
 }
 
-template <int ROWS>
+__device__ __forceinline__ void cp_async16(float* smem, const float* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem));
+}
+
+// ROWS: state rows a thread holds; TPR: tokens per staging round
+template <int ROWS, int TPR>
 __global__ void __launch_bounds__(THREADS)
 linear_recurrence_kernel(const RecurrenceArgs p) {
   extern __shared__ float smem[];
@@ -119,7 +124,8 @@ linear_recurrence_kernel(const RecurrenceArgs p) {
   const int col = blockIdx.x * p.cols_per_block + col_local;
   const bool col_ok = col < p.vdim;
   const int dpad = p.slices * ROWS;  // state rows covered by the threads of a column (>= dim)
-  const int R = p.tokens_per_round, C = p.cols_per_block;
+  constexpr int R = TPR;
+  const int C = p.cols_per_block;
   const bool gate = p.mode == FORGET_GATE;
   const int planes = gate ? 3 : 2;
   // one staging buffer: [planes][R][dpad] then v [R][C]; two of them when rounds arrive by cp.async
@@ -141,11 +147,18 @@ linear_recurrence_kernel(const RecurrenceArgs p) {
     for (int idx = tid; idx < (p.ready ? 2 : 1) * buf_floats; idx += THREADS) smem[idx] = 0.f;
   __syncthreads();
 
+  // rows of 16-byte pieces where every address allows it, single floats otherwise
+  const bool wide = p.dim % 4 == 0 && (((uintptr_t)p.ready) & 15) == 0;
   auto stage_async = [&](int base, float* buf) {
     const int n = min(R, t1 - base);
-    for (int idx = tid; idx < planes * n * p.dim; idx += THREADS) {
-      const int pl = idx / (n * p.dim), rem = idx % (n * p.dim), r = rem / p.dim, i = rem % p.dim;
-      cp_async4(buf + (pl * R + r) * dpad + i, p.ready + ((size_t)(base + r) * planes + pl) * hd + head * p.dim + i);
+    for (int row = tid >> 5; row < planes * n; row += THREADS / 32) {
+      const int pl = row / n, r = row % n;
+      float* dst = buf + (pl * R + r) * dpad;
+      const float* src = p.ready + ((size_t)(base + r) * planes + pl) * hd + head * p.dim;
+      if (wide)
+        for (int i = (tid & 31) * 4; i < p.dim; i += 128) cp_async16(dst + i, src + i);
+      else
+        for (int i = tid & 31; i < p.dim; i += 32) cp_async4(dst + i, src + i);
     }
     asm volatile("cp.async.commit_group;\n");
   };
@@ -187,7 +200,7 @@ linear_recurrence_kernel(const RecurrenceArgs p) {
       stage_values(base, buf);
     }
     __syncthreads();
-    for (int r = 0; r < n; ++r) {
+    auto one_token = [&](int r) {
       const float v = vs[r * C + col_local];
       const float* qr = qs + r * dpad + slice;
       const float* br = bs + r * dpad + slice;
@@ -210,9 +223,30 @@ linear_recurrence_kernel(const RecurrenceArgs p) {
           acc1 = fmaf(S[k + 1], qr[p.slices * (k + 1)], acc1);
         }
       }
-      float acc = acc0 + acc1;
-      for (int o = 1; o < p.slices; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (slice == 0) os[r * C + col_local] = acc;
+      return acc0 + acc1;
+    };
+    if (n == R) {
+      // a full round: the tokens' partial outputs first, then their reductions over the slices
+      // side by side (the shuffles of one token do not wait for another's)
+      float acc[R];
+#pragma unroll
+      for (int r = 0; r < R; ++r) acc[r] = one_token(r);
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1)
+        if (o < p.slices) {
+#pragma unroll
+          for (int r = 0; r < R; ++r) acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], o);
+        }
+      if (slice == 0) {
+#pragma unroll
+        for (int r = 0; r < R; ++r) os[r * C + col_local] = acc[r];
+      }
+    } else {
+      for (int r = 0; r < n; ++r) {
+        float acc = one_token(r);
+        for (int o = 1; o < p.slices; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (slice == 0) os[r * C + col_local] = acc;
+      }
     }
     __syncthreads();
     for (int idx = tid; idx < n * C; idx += THREADS) {
@@ -227,15 +261,15 @@ linear_recurrence_kernel(const RecurrenceArgs p) {
   }
 }
 
-template <int ROWS>
+template <int ROWS, int TPR>
 int launch(const RecurrenceArgs& a, int S, size_t smem, cudaStream_t stream) {
   static size_t configured = 48 * 1024;
   if (smem > configured) {
-    DSP_CUDA(cudaFuncSetAttribute(linear_recurrence_kernel<ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    DSP_CUDA(cudaFuncSetAttribute(linear_recurrence_kernel<ROWS, TPR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = smem;
   }
   dim3 grid((a.vdim + a.cols_per_block - 1) / a.cols_per_block, a.H, S);
-  linear_recurrence_kernel<ROWS><<<grid, THREADS, smem, stream>>>(a);
+  linear_recurrence_kernel<ROWS, TPR><<<grid, THREADS, smem, stream>>>(a);
   DSP_CHECK_LAUNCH("dsp_linear_recurrence");
   return 0;
 }
@@ -294,7 +328,12 @@ extern "C" int dsp_linear_recurrence(const void* proj, int proj_dtype, long ld, 
     recurrence_prepare_kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, stream>>>(a, T);
     DSP_CHECK_LAUNCH("dsp_linear_recurrence (first kernel)");
   }
-  if (R == 8) return launch<8>(a, S, smem, stream);
-  if (R == 16) return launch<16>(a, S, smem, stream);
-  return launch<32>(a, S, smem, stream);
+  if (a.tokens_per_round == 16) {
+    if (R == 8) return launch<8, 16>(a, S, smem, stream);
+    if (R == 16) return launch<16, 16>(a, S, smem, stream);
+    return launch<32, 16>(a, S, smem, stream);
+  }
+  if (R == 8) return launch<8, 8>(a, S, smem, stream);
+  if (R == 16) return launch<16, 8>(a, S, smem, stream);
+  return launch<32, 8>(a, S, smem, stream);
 }
