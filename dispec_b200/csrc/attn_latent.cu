@@ -288,7 +288,8 @@ extern "C" int dsp_attn_latent(const float* qa, long ldqa, const void* q, int q_
 // key tile it loads among all its rows.  Keys come in tiles of 32 through the page table
 // (cp.async, two buffers); a key row is [latent R | rotated part r] in shared memory and its
 // first R values are the value row as well.  16 warps = 4 row groups x 4 column groups:
-//   S = Q K^T   warp (rg, cg) forms the 16 x 8 block of its rows and keys cg*8.. over the depth R + r
+//   S = Q K^T   warp (rg, cg) multiplies its 16 rows with all 32 keys over a quarter of the depth R + r;
+//               the quarters are added in shared memory, where each warp picks up keys cg*8..
 //   softmax     row maxima and sums of the four column groups meet in shared memory; P goes there
 //               as bfloat16 (the sums are taken before the rounding)
 //   O += P V    warp (rg, cg) owns the R / 4 output columns cg * R/4 .. of its rows
@@ -297,7 +298,7 @@ extern "C" int dsp_attn_latent(const float* qa, long ldqa, const void* q, int q_
 // with long contexts then fill the device.  Keys beyond the tile's last position are never
 // loaded (zero rows); a page id outside the pool is recorded and its rows are zero.
 namespace tc {
-constexpr int BM = 64, BN = 32, THREADS = 512, P_ROWB = 80;
+constexpr int BM = 64, BN = 32, THREADS = 512, P_ROWB = 80, S_ROW = BN + 4;
 
 struct Args {
   const float* qa; long ldqa;
@@ -353,6 +354,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_latent_mma_kernel(const Args 
   const uint32_t p_s = k_s + 2 * BN * ROWB;
   float* red_max = reinterpret_cast<float*>(smem + (size_t)BM * ROWB + 2 * (size_t)BN * ROWB + BM * P_ROWB);  // [BM][4]
   float* red_sum = red_max + BM * 4;                                                                          // [BM][4]
+  float* s_part = red_sum + BM * 4;  // [4][BM][S_ROW]: the column groups' partial scores
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int rg = warp & 3, cg = warp >> 2;
   const int tile = blockIdx.x + p.tile_offset;
@@ -378,23 +380,35 @@ __global__ void __launch_bounds__(THREADS, 1) attn_latent_mma_kernel(const Args 
     return;
   }
 
+  // a thread's pieces of a key tile: first every page id (independent loads), then the copies
+  constexpr int MAX_PIECES = 8;  // BN * CH / THREADS: depth up to 1024 + 64
   auto load_keys = [&](int kt, int buf) {
-    for (int c = tid; c < BN * CH; c += THREADS) {
-      const int row = c / CH, ch = c % CH;
-      const int key = kt * BN + row;
-      bool valid = key <= hi;
-      long at = 0;
-      if (valid) {
-        const int page = table[key / p.page_size];
-        if (page < 0 || page >= p.num_pages) {
-          atomicOr(p.err, DSP_ERR_BAD_PAGE);
-          valid = false;
-        } else {
-          at = (long)page * p.page_size + key % p.page_size;
+    long at[MAX_PIECES];
+#pragma unroll
+    for (int it = 0; it < MAX_PIECES; ++it) {
+      const int c = tid + it * THREADS;
+      at[it] = -1;
+      if (c < BN * CH) {
+        const int key = kt * BN + c / CH;
+        if (key <= hi) {
+          const int page = table[key / p.page_size];
+          if (page < 0 || page >= p.num_pages)
+            atomicOr(p.err, DSP_ERR_BAD_PAGE);
+          else
+            at[it] = (long)page * p.page_size + key % p.page_size;
         }
       }
-      const bf16* src = ch < CH_LAT ? p.c_pool + at * p.R + ch * 8 : p.r_pool + at * p.r + (ch - CH_LAT) * 8;
-      cp_async16(k_s + (buf * BN + row) * ROWB + ch * 16, src, valid);
+    }
+#pragma unroll
+    for (int it = 0; it < MAX_PIECES; ++it) {
+      const int c = tid + it * THREADS;
+      if (c < BN * CH) {
+        const int row = c / CH, ch = c % CH;
+        const bool valid = at[it] >= 0;
+        const long a0 = valid ? at[it] : 0;
+        const bf16* src = ch < CH_LAT ? p.c_pool + a0 * p.R + ch * 8 : p.r_pool + a0 * p.r + (ch - CH_LAT) * 8;
+        cp_async16(k_s + (buf * BN + row) * ROWB + ch * 16, src, valid);
+      }
     }
     cp_async_commit();
   };
@@ -445,12 +459,40 @@ __global__ void __launch_bounds__(THREADS, 1) attn_latent_mma_kernel(const Args 
     }
     __syncthreads();
     const uint32_t kbuf = k_s + buf * BN * ROWB;
-    float s[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int kk = 0; kk < W / 16; ++kk) {
-      uint32_t a[4], b[2];
+    // scores: warp (rg, cg) takes a quarter of the depth for all 32 keys of the tile (one query
+    // fragment per four mma), the four partial blocks meet in shared memory
+    float sp[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) sp[i][e] = 0.f;
+    const int KS = W / 16, k_per = (KS + 3) / 4, k_lo = cg * k_per, k_hi = min(KS, k_lo + k_per);
+    for (int kk = k_lo; kk < k_hi; ++kk) {
+      uint32_t a[4];
       ldmatrix_x4(a, q_s + (rg * 16 + (m8 & 1) * 8 + l8) * ROWB + (kk * 2 + (m8 >> 1)) * 16);
-      ldmatrix_x2(b, kbuf + (cg * 8 + l8) * ROWB + (kk * 2 + (m8 & 1)) * 16);
-      mma_bf16(s, a, b[0], b[1]);
+#pragma unroll
+      for (int nn = 0; nn < 2; ++nn) {
+        uint32_t b[4];
+        ldmatrix_x4(b, kbuf + (nn * 16 + (m8 >> 1) * 8 + l8) * ROWB + (kk * 2 + (m8 & 1)) * 16);
+        mma_bf16(sp[2 * nn], a, b[0], b[1]);
+        mma_bf16(sp[2 * nn + 1], a, b[2], b[3]);
+      }
+    }
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      *reinterpret_cast<float2*>(s_part + ((cg * BM + row_a) * S_ROW + nt * 8 + 2 * c4)) = make_float2(sp[nt][0], sp[nt][1]);
+      *reinterpret_cast<float2*>(s_part + ((cg * BM + row_b) * S_ROW + nt * 8 + 2 * c4)) = make_float2(sp[nt][2], sp[nt][3]);
+    }
+    __syncthreads();
+    float s[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {  // the quarters in a fixed order
+      const float2 va = *reinterpret_cast<const float2*>(s_part + ((c * BM + row_a) * S_ROW + cg * 8 + 2 * c4));
+      const float2 vb = *reinterpret_cast<const float2*>(s_part + ((c * BM + row_b) * S_ROW + cg * 8 + 2 * c4));
+      s[0] += va.x;
+      s[1] += va.y;
+      s[2] += vb.x;
+      s[3] += vb.y;
     }
     const int key0 = kt * BN + cg * 8 + 2 * c4;
     s[0] = key0 <= pos_a ? s[0] * p.scale_log2 : -INFINITY;
@@ -547,7 +589,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_latent_mma_kernel(const Args 
 template <int NT16>
 int launch(const Args& a, int num_tiles, int head_chunks, cudaStream_t stream) {
   const int ROWB = key_row_bytes(a.R + a.r);
-  const size_t smem = (size_t)BM * ROWB + 2 * (size_t)BN * ROWB + BM * P_ROWB + 2 * BM * 4 * sizeof(float);
+  const size_t smem = (size_t)BM * ROWB + 2 * (size_t)BN * ROWB + BM * P_ROWB + (2 * BM * 4 + 4 * BM * S_ROW) * sizeof(float);
   if (smem > 227 * 1024) return 2;
   static bool configured = false;
   if (!configured) {
@@ -577,6 +619,7 @@ extern "C" int dsp_attn_latent_mma(const float* qa, long ldqa, const void* q, in
   int* err = dsp_device_error_ptr();
   DSP_REQUIRE(err != nullptr, "dsp_attn_latent_mma: no device error word");
   DSP_REQUIRE(R % 64 == 0 && r % 16 == 0 && r >= 0 && rot % 2 == 0 && rot <= r, "dsp_attn_latent_mma: R=%d r=%d rot=%d", R, r, rot);
+  DSP_REQUIRE(tc::BN * ((R + r) / 8) <= 8 * tc::THREADS, "dsp_attn_latent_mma: key rows of %d values are too wide", R + r);
   DSP_REQUIRE(ldqa % 2 == 0 && ((uintptr_t)qa % 8) == 0 && ldo % 2 == 0 && ((uintptr_t)out % 4) == 0 &&
               ((uintptr_t)c_pool % 16) == 0 && ((uintptr_t)r_pool % 16) == 0, "dsp_attn_latent_mma: operand alignment");
   DSP_REQUIRE(splits >= 1 && (splits == 1 || (part_o && part_ml)), "dsp_attn_latent_mma: splits=%d without scratch", splits);

@@ -81,7 +81,7 @@ def mma_supported(kv_rank: int, rot_dim: int, pool_dtype: torch.dtype) -> bool:
         return False
     row_bytes = ((2 * (kv_rank + rot_dim) + 127) // 128) * 128 + 16
     return (pool_dtype == torch.bfloat16 and kv_rank in _MMA_LATENT_SIZES and rot_dim % 16 == 0
-            and 128 * row_bytes + 64 * 80 + 2048 <= 227 * 1024)
+            and 128 * row_bytes + 64 * 80 + 2048 + 4 * 64 * 36 * 4 <= 227 * 1024)
 
 
 def choose_key_splits(num_tiles: int, head_chunks: int, max_ctx: int, device) -> int:
