@@ -380,65 +380,63 @@ __global__ void __launch_bounds__(THREADS, 1) attn_latent_mma_kernel(const Args 
     return;
   }
 
-  // a thread's pieces of a key tile: first every page id (independent loads), then the copies
-  constexpr int MAX_PIECES = 8;  // BN * CH / THREADS: depth up to 1024 + 64
+  // a warp copies whole key rows (two of the tile's 32): one page lookup and one division a row,
+  // the lanes take the row's 16-byte pieces
   auto load_keys = [&](int kt, int buf) {
-    long at[MAX_PIECES];
 #pragma unroll
-    for (int it = 0; it < MAX_PIECES; ++it) {
-      const int c = tid + it * THREADS;
-      at[it] = -1;
-      if (c < BN * CH) {
-        const int key = kt * BN + c / CH;
-        if (key <= hi) {
-          const int page = table[key / p.page_size];
-          if (page < 0 || page >= p.num_pages)
-            atomicOr(p.err, DSP_ERR_BAD_PAGE);
-          else
-            at[it] = (long)page * p.page_size + key % p.page_size;
+    for (int rr = 0; rr < BN / (THREADS / 32); ++rr) {
+      const int row = warp + rr * (THREADS / 32);
+      const int key = kt * BN + row;
+      long at = -1;
+      if (key <= hi) {
+        const int page = table[key / p.page_size];
+        if (page < 0 || page >= p.num_pages) {
+          if (lane == 0) atomicOr(p.err, DSP_ERR_BAD_PAGE);
+        } else {
+          at = (long)page * p.page_size + key % p.page_size;
         }
       }
-    }
-#pragma unroll
-    for (int it = 0; it < MAX_PIECES; ++it) {
-      const int c = tid + it * THREADS;
-      if (c < BN * CH) {
-        const int row = c / CH, ch = c % CH;
-        const bool valid = at[it] >= 0;
-        const long a0 = valid ? at[it] : 0;
-        const bf16* src = ch < CH_LAT ? p.c_pool + a0 * p.R + ch * 8 : p.r_pool + a0 * p.r + (ch - CH_LAT) * 8;
-        cp_async16(k_s + (buf * BN + row) * ROWB + ch * 16, src, valid);
-      }
+      const bool valid = at >= 0;
+      const bf16* c_src = p.c_pool + (valid ? at : 0) * p.R;
+      const bf16* r_src = p.r_pool + (valid ? at : 0) * p.r;
+      const uint32_t dst = k_s + (buf * BN + row) * ROWB;
+      for (int ch = lane; ch < CH; ch += 32)
+        cp_async16(dst + ch * 16, ch < CH_LAT ? c_src + ch * 8 : r_src + (ch - CH_LAT) * 8, valid);
     }
     cp_async_commit();
   };
   load_keys(kb, 0);
 
-  // the query rows as bfloat16: [absorbed query | rotated part], zero beyond the tile's rows
-  for (int idx = tid; idx < BM * (W / 2); idx += THREADS) {
-    const int m = idx / (W / 2), d = (idx % (W / 2)) * 2;
-    float v0 = 0.f, v1 = 0.f;
-    if (m < nrows) {
-      const int t = qs + tok0 + m / hc, hd = head0 + m % hc;
-      if (d < p.R) {
-        const float2 v = *reinterpret_cast<const float2*>(p.qa + (size_t)t * p.ldqa + (size_t)hd * p.R + d);
-        v0 = v.x;
-        v1 = v.y;
-      } else {
-        const int j = d - p.R;
-        const size_t at = (size_t)t * p.ldq + (size_t)hd * p.q_head_stride + p.qr_off;
-        v0 = ld_any(p.q, p.q_dtype, at + j);
-        v1 = ld_any(p.q, p.q_dtype, at + j + 1);
-        if (j < p.rot) {
-          float sn, cs;
-          sincosf((float)(pos0 + m / hc) * p.inv_freq[j >> 1], &sn, &cs);
-          const float u = v0, w = v1;
-          v0 = u * cs - w * sn;
-          v1 = w * cs + u * sn;
+  // the query rows as bfloat16: [absorbed query | rotated part], zero beyond the tile's rows;
+  // a warp takes whole rows, its lanes pairs of values
+  for (int m = warp; m < BM; m += THREADS / 32) {
+    const bool real = m < nrows;
+    const int tk = real ? m / hc : 0;
+    const int t = qs + tok0 + tk, hd = head0 + (real ? m % hc : 0);
+    const float* qa_row = p.qa + (size_t)t * p.ldqa + (size_t)hd * p.R;
+    const size_t at = (size_t)t * p.ldq + (size_t)hd * p.q_head_stride + p.qr_off;
+    for (int d = lane * 2; d < W; d += 64) {
+      float v0 = 0.f, v1 = 0.f;
+      if (real) {
+        if (d < p.R) {
+          const float2 v = *reinterpret_cast<const float2*>(qa_row + d);
+          v0 = v.x;
+          v1 = v.y;
+        } else {
+          const int j = d - p.R;
+          v0 = ld_any(p.q, p.q_dtype, at + j);
+          v1 = ld_any(p.q, p.q_dtype, at + j + 1);
+          if (j < p.rot) {
+            float sn, cs;
+            sincosf((float)(pos0 + tk) * p.inv_freq[j >> 1], &sn, &cs);
+            const float u = v0, w = v1;
+            v0 = u * cs - w * sn;
+            v1 = w * cs + u * sn;
+          }
         }
       }
+      *reinterpret_cast<uint32_t*>(smem + (size_t)m * ROWB + d * 2) = pack_bf16(v0, v1);
     }
-    *reinterpret_cast<uint32_t*>(smem + (size_t)m * ROWB + d * 2) = pack_bf16(v0, v1);
   }
 
   float o[2 * NT16][4];
@@ -619,7 +617,6 @@ extern "C" int dsp_attn_latent_mma(const float* qa, long ldqa, const void* q, in
   int* err = dsp_device_error_ptr();
   DSP_REQUIRE(err != nullptr, "dsp_attn_latent_mma: no device error word");
   DSP_REQUIRE(R % 64 == 0 && r % 16 == 0 && r >= 0 && rot % 2 == 0 && rot <= r, "dsp_attn_latent_mma: R=%d r=%d rot=%d", R, r, rot);
-  DSP_REQUIRE(tc::BN * ((R + r) / 8) <= 8 * tc::THREADS, "dsp_attn_latent_mma: key rows of %d values are too wide", R + r);
   DSP_REQUIRE(ldqa % 2 == 0 && ((uintptr_t)qa % 8) == 0 && ldo % 2 == 0 && ((uintptr_t)out % 4) == 0 &&
               ((uintptr_t)c_pool % 16) == 0 && ((uintptr_t)r_pool % 16) == 0, "dsp_attn_latent_mma: operand alignment");
   DSP_REQUIRE(splits >= 1 && (splits == 1 || (part_o && part_ml)), "dsp_attn_latent_mma: splits=%d without scratch", splits);
