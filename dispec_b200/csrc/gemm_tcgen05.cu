@@ -95,6 +95,23 @@ __device__ __forceinline__ void store_row_chunk(const Epilogue& e, const uint32_
       }
       reinterpret_cast<uint4*>(dst)[j] = oraw;
     }
+  } else if (valid == 32 && sizeof(TOut) == 4 && (((uintptr_t)dst | (uintptr_t)res) % 16) == 0) {
+    // 32-bit output: the same sums in the same order, stored 16 bytes at a time
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float4 r4 = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (res) r4 = reinterpret_cast<const float4*>(res)[j];
+      const float rr[4] = {r4.x, r4.y, r4.z, r4.w};
+      float o[4];
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        float x = __uint_as_float(v[j * 4 + t]);
+        if (e.bias) x += __bfloat162float(e.bias[col + j * 4 + t]);
+        if (res) x += rr[t];
+        o[t] = x;
+      }
+      reinterpret_cast<float4*>(dst)[j] = make_float4(o[0], o[1], o[2], o[3]);
+    }
   } else {
 #pragma unroll  // constant indices: a loop up to `valid` would put the accumulators into local memory on every path
     for (int t = 0; t < 32; ++t) {

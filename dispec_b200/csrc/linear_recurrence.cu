@@ -151,15 +151,15 @@ linear_recurrence_kernel(const RecurrenceArgs p) {
   const bool wide = p.dim % 4 == 0 && (((uintptr_t)p.ready) & 15) == 0;
   auto stage_async = [&](int base, float* buf) {
     const int n = min(R, t1 - base);
-    for (int row = tid >> 5; row < planes * n; row += THREADS / 32) {
-      const int pl = row / n, r = row % n;
-      float* dst = buf + (pl * R + r) * dpad;
-      const float* src = p.ready + ((size_t)(base + r) * planes + pl) * hd + head * p.dim;
-      if (wide)
-        for (int i = (tid & 31) * 4; i < p.dim; i += 128) cp_async16(dst + i, src + i);
-      else
-        for (int i = tid & 31; i < p.dim; i += 32) cp_async4(dst + i, src + i);
-    }
+    for (int pl = 0; pl < planes; ++pl)
+      for (int r = tid >> 5; r < n; r += THREADS / 32) {
+        float* dst = buf + (pl * R + r) * dpad;
+        const float* src = p.ready + ((size_t)(base + r) * planes + pl) * hd + head * p.dim;
+        if (wide)
+          for (int i = (tid & 31) * 4; i < p.dim; i += 128) cp_async16(dst + i, src + i);
+        else
+          for (int i = tid & 31; i < p.dim; i += 32) cp_async4(dst + i, src + i);
+      }
     asm volatile("cp.async.commit_group;\n");
   };
   auto stage_values = [&](int base, float* buf) {
