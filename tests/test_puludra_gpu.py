@@ -331,7 +331,8 @@ def test_latent_store_kernel_norms_rotates_and_places():
     assert int(torch.isfinite(c_pool[:, 0, :, 0]).sum()) == written  # nothing else was touched
 
 
-@pytest.mark.parametrize("H,R,r,page", [(10, 192, 16, 16), (12, 512, 64, 16), (70, 64, 32, 8), (3, 128, 0, 32)])
+@pytest.mark.parametrize("H,R,r,page", [(10, 192, 16, 16), (12, 512, 64, 16), (70, 64, 32, 8), (3, 128, 0, 32),
+                                        (5, 256, 48, 16), (2, 384, 16, 64), (4, 128, 32, 16)])
 def test_latent_attention_on_tensor_cores_matches_the_plain_softmax(H, R, r, page):
     """The tensor-core kernel over a step of two single tokens (keys cut into ranges and merged)
     and a portion of a prompt whose tiles end in the middle of a key tile; every query is aimed at
