@@ -5,13 +5,15 @@
 //     max(0, p - window + 1) <= b <= p        (window == 0: every key from 0)
 // which is the lower-right aligned causal mask for a portion of a prompt on top of cached
 // tokens, and a single decoded token alike.  Online softmax (running max m, running sum l)
-// over tiles of 128 keys.  Any head_dim that is a multiple of 4 (float) / 8 (bfloat16) up to
+// over tiles of 128 keys.  Keys have D dimensions and values Dv (the pools have their own widths).
+// With `sink` the softmax has one more, imaginary key of score 0 and no value: the weights are
+// exp(s_j) / (1 + sum exp(s_j)); the running pair starts at (m, l) = (0, 1) instead of (-inf, 0).  Any head_dim that is a multiple of 4 (float) / 8 (bfloat16) up to
 // 512, any G.  This kernel is the attention of the 32-bit path and the fallback of the
 // bfloat16 path for head sizes the tensor-core kernel is not built for.
 //
 // q:   element (t, head, d) at q[t * q_stride + head * D + d]
-// out: element (t, head, d) at out[t * out_stride + head * D + d]
-// pools: [num_pages, KVH, page_size, D]; page = page_table[seq * pt_stride + b / page_size]
+// out: element (t, head, d) at out[t * out_stride + head * Dv + d]
+// pools: [num_pages, KVH, page_size, D] (keys) and [..., Dv] (values); page = page_table[seq * pt_stride + b / page_size]
 #include "common.cuh"
 
 namespace {
@@ -25,12 +27,12 @@ attn_generic_kernel(const T* __restrict__ q, long q_stride, const T* __restrict_
                     const T* __restrict__ v_pool, const int* __restrict__ page_table,
                     int pt_stride, const int* __restrict__ positions,
                     const int* __restrict__ seq_of_token, T* __restrict__ out, long out_stride,
-                    int H, int KVH, int D, int page_size, int num_pages, int window, float scale,
-                    int* err) {
+                    int H, int KVH, int D, int Dv, int page_size, int num_pages, int window, float scale,
+                    int sink, int* err) {
   extern __shared__ float smem[];
   float* qs = smem;                       // [GCHUNK][D]
   float* ps = qs + GCHUNK * D;            // [GCHUNK][THREADS]
-  long* slot = (long*)(ps + GCHUNK * THREADS);  // [THREADS] element offset of each key row
+  long* slot = (long*)(ps + GCHUNK * THREADS);  // [THREADS] row of each key in the pools (-1: none)
   __shared__ float red[GCHUNK][THREADS / 32];
 
   const int t = blockIdx.x, kvh = blockIdx.y;
@@ -53,8 +55,8 @@ attn_generic_kernel(const T* __restrict__ q, long q_stride, const T* __restrict_
     float m[GCHUNK], l[GCHUNK], acc[GCHUNK][DPT];
 #pragma unroll
     for (int g = 0; g < GCHUNK; ++g) {
-      m[g] = -INFINITY;
-      l[g] = 0.f;
+      m[g] = sink ? 0.f : -INFINITY;
+      l[g] = sink ? 1.f : 0.f;
 #pragma unroll
       for (int j = 0; j < DPT; ++j) acc[g][j] = 0.f;
     }
@@ -72,8 +74,8 @@ attn_generic_kernel(const T* __restrict__ q, long q_stride, const T* __restrict_
         if (page < 0 || page >= num_pages) {
           atomicOr(err, DSP_ERR_BAD_PAGE);
         } else {
-          off = (((long)page * KVH + kvh) * page_size + (key % page_size)) * D;
-          const T* kr = k_pool + off;
+          off = ((long)page * KVH + kvh) * page_size + (key % page_size);
+          const T* kr = k_pool + off * D;
 #pragma unroll
           for (int g = 0; g < GCHUNK; ++g) s[g] = 0.f;
           for (int d = 0; d < D; ++d) {
@@ -126,11 +128,11 @@ attn_generic_kernel(const T* __restrict__ q, long q_stride, const T* __restrict_
       for (int j = 0; j < nkeys; ++j) {
         const long vo = slot[j];
         if (vo < 0) continue;
-        const T* vr = v_pool + vo;
+        const T* vr = v_pool + vo * Dv;
 #pragma unroll
         for (int dd = 0; dd < DPT; ++dd) {
           const int d = tid + dd * THREADS;
-          if (d < D) {
+          if (d < Dv) {
             const float vv = to_f32(vr[d]);
 #pragma unroll
             for (int g = 0; g < GCHUNK; ++g)
@@ -147,8 +149,8 @@ attn_generic_kernel(const T* __restrict__ q, long q_stride, const T* __restrict_
 #pragma unroll
       for (int dd = 0; dd < DPT; ++dd) {
         const int d = tid + dd * THREADS;
-        if (d < D)
-          out[(size_t)t * out_stride + (size_t)(kvh * G + g0 + g) * D + d] =
+        if (d < Dv)
+          out[(size_t)t * out_stride + (size_t)(kvh * G + g0 + g) * Dv + d] =
               from_f32<T>(acc[g][dd] * inv);
       }
     }
@@ -159,12 +161,13 @@ attn_generic_kernel(const T* __restrict__ q, long q_stride, const T* __restrict_
 extern "C" int dsp_attn_generic(const void* q, long q_stride, const void* k_pool,
                                 const void* v_pool, const int* page_table, int pt_stride,
                                 const int* positions, const int* seq_of_token, void* out,
-                                long out_stride, int T, int H, int KVH, int D, int page_size,
-                                int num_pages, int window, float scale, int dtype,
+                                long out_stride, int T, int H, int KVH, int D, int Dv, int page_size,
+                                int num_pages, int window, float scale, int sink, int dtype,
                                 cudaStream_t stream) {
   if (T == 0) return 0;
   DSP_REQUIRE(KVH > 0 && H % KVH == 0, "dsp_attn_generic: H=%d is not a multiple of KVH=%d", H, KVH);
-  DSP_REQUIRE(D > 0 && D <= THREADS * DPT, "dsp_attn_generic: head_dim=%d outside (0, %d]", D,
+  DSP_REQUIRE(D > 0 && Dv > 0 && Dv <= THREADS * DPT && D <= 4096,
+              "dsp_attn_generic: key size %d or value size %d outside the kernel's range (values up to %d)", D, Dv,
               THREADS * DPT);
   DSP_REQUIRE(KVH <= 65535, "dsp_attn_generic: too many KV heads");
   int* err = dsp_device_error_ptr();
@@ -180,8 +183,8 @@ extern "C" int dsp_attn_generic(const void* q, long q_stride, const void* k_pool
     }
     attn_generic_kernel<float><<<grid, THREADS, smem, stream>>>(
         (const float*)q, q_stride, (const float*)k_pool, (const float*)v_pool, page_table, pt_stride,
-        positions, seq_of_token, (float*)out, out_stride, H, KVH, D, page_size, num_pages, window,
-        scale, err);
+        positions, seq_of_token, (float*)out, out_stride, H, KVH, D, Dv, page_size, num_pages, window,
+        scale, sink, err);
   } else if (dtype == DSP_BF16) {
     static size_t configured = 0;
     if (smem > configured) {
@@ -191,8 +194,8 @@ extern "C" int dsp_attn_generic(const void* q, long q_stride, const void* k_pool
     }
     attn_generic_kernel<bf16><<<grid, THREADS, smem, stream>>>(
         (const bf16*)q, q_stride, (const bf16*)k_pool, (const bf16*)v_pool, page_table, pt_stride,
-        positions, seq_of_token, (bf16*)out, out_stride, H, KVH, D, page_size, num_pages, window,
-        scale, err);
+        positions, seq_of_token, (bf16*)out, out_stride, H, KVH, D, Dv, page_size, num_pages, window,
+        scale, sink, err);
   } else {
     DSP_REQUIRE(false, "dsp_attn_generic: unknown dtype %d", dtype);
   }

@@ -175,7 +175,8 @@ def prefill_attention_library(head_dim: int) -> str:
 
 # Kernels only some mixers need, each a library of its own that is built when a model with such
 # a mixer first runs: name -> source file.
-MIXER_LIBRARIES = {"linear_recurrence": "linear_recurrence.cu", "attn_latent": "attn_latent.cu"}
+MIXER_LIBRARIES = {"linear_recurrence": "linear_recurrence.cu", "attn_latent": "attn_latent.cu",
+                   "attn_sink": "attn_sink.cu", "moe": "moe.cu"}
 
 
 def mixer_library(name: str) -> str:

@@ -10,7 +10,8 @@
 //
 //   FIXED_DECAY   a_t = decay[head] (one number per head); q_t and b_t are the projected query
 //                 and key with pairs (i, i + rot/2) of their first `rot` dimensions turned by
-//                 the angle position * inv_freq[i], and b_t scaled by `key_scale` afterwards
+//                 the angle position * inv_freq[i], and b_t scaled by `key_scale` afterwards;
+//                 with `act` = 1 the raw query, key and value pass through silu first
 //   FORGET_GATE   a_t = f_t = lower + (1 - lower) * sigmoid(raw_f + bias), b_t = 1 - f_t,
 //                 q_t = silu(raw_q)      (lower and bias per head and channel)
 //
@@ -41,6 +42,7 @@ struct RecurrenceArgs {
   const float* inv_freq;  // [rot / 2]            FIXED_DECAY (may be null when rot == 0)
   int rot;
   float key_scale;
+  int act;  // 1: silu on the raw query, key and value (FIXED_DECAY)
   const float* gate_bias;  // [H * dim]           FORGET_GATE
   const float* lower;      // [H * dim]           FORGET_GATE
   float* state;            // [slots, H, dim, vdim]
@@ -64,14 +66,22 @@ __device__ __forceinline__ void transform(const RecurrenceArgs& p, int token, in
   if (p.mode == FIXED_DECAY) {
     qv = ld_any(p.proj, p.proj_dtype, qo + i);
     bv = ld_any(p.proj, p.proj_dtype, ko + i);
+    if (p.act == 1) {
+      qv = qv / (1.f + expf(-qv));
+      bv = bv / (1.f + expf(-bv));
+    }
     if (i < p.rot) {
       const int half = p.rot / 2;
       const int f = i < half ? i : i - half;
       const int other = i < half ? i + half : i - half;
       float sn, cs;
       sincosf((float)p.positions[token] * p.inv_freq[f], &sn, &cs);
-      const float q2 = ld_any(p.proj, p.proj_dtype, qo + other);
-      const float k2 = ld_any(p.proj, p.proj_dtype, ko + other);
+      float q2 = ld_any(p.proj, p.proj_dtype, qo + other);
+      float k2 = ld_any(p.proj, p.proj_dtype, ko + other);
+      if (p.act == 1) {
+        q2 = q2 / (1.f + expf(-q2));
+        k2 = k2 / (1.f + expf(-k2));
+      }
       // first of the pair: u cos - v sin; second: v cos + u sin
       qv = i < half ? qv * cs - q2 * sn : qv * cs + q2 * sn;
       bv = i < half ? bv * cs - k2 * sn : bv * cs + k2 * sn;
@@ -167,7 +177,9 @@ linear_recurrence_kernel(const RecurrenceArgs p) {
     float* vs = buf + planes * R * dpad;
     for (int idx = tid; idx < n * C; idx += THREADS) {
       const int r = idx / C, c = blockIdx.x * C + idx % C;
-      vs[idx] = c < p.vdim ? ld_any(p.proj, p.proj_dtype, (size_t)(base + r) * p.ld + p.v_off + (size_t)head * p.vdim + c) : 0.f;
+      float v = c < p.vdim ? ld_any(p.proj, p.proj_dtype, (size_t)(base + r) * p.ld + p.v_off + (size_t)head * p.vdim + c) : 0.f;
+      if (p.act == 1) v = v / (1.f + expf(-v));
+      vs[idx] = v;
     }
   };
 
@@ -284,7 +296,7 @@ extern "C" long dsp_linear_recurrence_scratch(int mode, int H, int dim, long T) 
 // dsp_linear_recurrence_scratch floats (a first kernel transforms every token, the recurrence streams).
 extern "C" int dsp_linear_recurrence(const void* proj, int proj_dtype, long ld, int q_off, int k_off,
                                      int v_off, int mode, int H, int dim, int vdim, const float* decay,
-                                     const float* inv_freq, int rot, float key_scale,
+                                     const float* inv_freq, int rot, float key_scale, int act,
                                      const float* gate_bias, const float* lower, float* state,
                                      const int* state_slot, const int* q_start, const int* positions,
                                      float* out, long ldo, int S, int T, float* scratch, cudaStream_t stream) {
@@ -295,6 +307,7 @@ extern "C" int dsp_linear_recurrence(const void* proj, int proj_dtype, long ld, 
   if (mode == FIXED_DECAY) {
     DSP_REQUIRE(decay != nullptr, "dsp_linear_recurrence: no decay");
     DSP_REQUIRE(rot >= 0 && rot <= dim && rot % 2 == 0 && (rot == 0 || inv_freq), "dsp_linear_recurrence: rot=%d", rot);
+    DSP_REQUIRE(act == 0 || act == 1, "dsp_linear_recurrence: unknown activation %d", act);
   } else if (mode == FORGET_GATE) {
     DSP_REQUIRE(gate_bias && lower, "dsp_linear_recurrence: no gate bias or lower bound");
   } else {
@@ -304,7 +317,7 @@ extern "C" int dsp_linear_recurrence(const void* proj, int proj_dtype, long ld, 
   a.proj = proj; a.proj_dtype = proj_dtype; a.ld = ld;
   a.q_off = q_off; a.k_off = k_off; a.v_off = v_off; a.mode = mode;
   a.H = H; a.dim = dim; a.vdim = vdim;
-  a.decay = decay; a.inv_freq = inv_freq; a.rot = rot; a.key_scale = key_scale;
+  a.decay = decay; a.inv_freq = inv_freq; a.rot = rot; a.key_scale = key_scale; a.act = mode == FIXED_DECAY ? act : 0;
   a.gate_bias = gate_bias; a.lower = lower;
   a.state = state; a.state_slot = state_slot; a.q_start = q_start; a.positions = positions;
   a.out = out; a.ldo = ldo; a.ready = scratch;

@@ -1,0 +1,277 @@
+// Mixture of experts: a router with groups of experts, and the experts' products over rows that
+// are sorted by expert on the device (no host round trip: every launch has a fixed upper bound of
+// tiles and blocks beyond the real number leave at once, so a step can be captured in a graph).
+//
+//   dsp_moe_route    scores = softmax(W_router h) over all experts in 32-bit (W_router float, h of
+//                    either type); experts form `groups` equal runs of neighbours, a group's score
+//                    is its largest score, only experts of the `keep` best groups can be chosen;
+//                    the `top` largest of those are the token's experts, their scores its weights
+//                    (not renormalised).  Equal scores: the lower index wins.  One warp per token.
+//   dsp_moe_plan     counts the (token, choice) pairs per expert, lists the pairs expert by expert
+//                    and cuts every expert's run into tiles of TILE_ROWS rows.  One block.
+//   dsp_moe_product  C[c_row(i)] = act(A[a_row(i)] B_e^T) for the sorted pairs i of every expert e
+//                    (B: [experts, N, K]); a_row / c_row are optional index lists (gather, scatter).
+//                    act 0: none, 1: the square of relu.  Every output is one chain of fused
+//                    multiply-adds in ascending k, so a pair's result depends on nothing but its own
+//                    row and its expert.
+//   dsp_moe_combine  y[t] = sum_k weight[t, k] * P[t * top + k], in ascending k.
+#include "common.cuh"
+
+namespace {
+constexpr int TILE_ROWS = 32, TILE_COLS = 64, TILE_K = 32;
+
+struct Best {
+  float v;
+  int i;
+};
+__device__ __forceinline__ Best better(Best a, Best b) {
+  if (b.i >= 0 && (a.i < 0 || b.v > a.v || (b.v == a.v && b.i < a.i))) return b;
+  return a;
+}
+__device__ __forceinline__ Best warp_best(Best b) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    Best other;
+    other.v = __shfl_xor_sync(0xffffffffu, b.v, o);
+    other.i = __shfl_xor_sync(0xffffffffu, b.i, o);
+    b = better(b, other);
+  }
+  return b;
+}
+
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const void* __restrict__ h, int h_dtype, long ldh, const float* __restrict__ w, int T, int W, int E,
+                 int groups, int keep, int top, int* __restrict__ ids, float* __restrict__ wts) {
+  extern __shared__ float sm[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long t = (long)blockIdx.x * (blockDim.x >> 5) + warp;
+  if (t >= T) return;
+  float* sc = sm + (size_t)warp * (2 * E + groups);  // scores
+  float* ok = sc + E;                               // 1: may still be chosen
+  float* gb = ok + E;                               // best score of each group
+  for (int e = 0; e < E; ++e) {
+    float acc = 0.f;
+    for (int i = lane; i < W; i += 32) acc = fmaf(w[(size_t)e * W + i], ld_any(h, h_dtype, (size_t)t * ldh + i), acc);
+    acc = warp_sum(acc);
+    if (lane == 0) sc[e] = acc;
+  }
+  __syncwarp();
+  float mx = -INFINITY;
+  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, sc[e]);
+  mx = warp_max(mx);
+  float sum = 0.f;
+  for (int e = lane; e < E; e += 32) sum += expf(sc[e] - mx);
+  sum = warp_sum(sum);
+  __syncwarp();
+  for (int e = lane; e < E; e += 32) {
+    sc[e] = expf(sc[e] - mx) / sum;
+    ok[e] = 0.f;
+  }
+  __syncwarp();
+  const int per = E / groups;
+  for (int g = lane; g < groups; g += 32) {
+    float b = -1.f;
+    for (int j = 0; j < per; ++j) b = fmaxf(b, sc[g * per + j]);
+    gb[g] = b;
+  }
+  __syncwarp();
+  for (int r = 0; r < keep; ++r) {
+    Best b = {-1.f, -1};
+    for (int g = lane; g < groups; g += 32) b = better(b, Best{gb[g], gb[g] >= 0.f ? g : -1});
+    b = warp_best(b);
+    if (b.i < 0) break;
+    for (int j = lane; j < per; j += 32) ok[b.i * per + j] = 1.f;
+    if (lane == 0) gb[b.i] = -1.f;
+    __syncwarp();
+  }
+  for (int r = 0; r < top; ++r) {
+    Best b = {-1.f, -1};
+    for (int e = lane; e < E; e += 32) b = better(b, Best{sc[e], ok[e] > 0.f ? e : -1});
+    b = warp_best(b);
+    if (lane == 0) {
+      ids[t * top + r] = b.i;
+      wts[t * top + r] = b.i >= 0 ? b.v : 0.f;
+      if (b.i >= 0) ok[b.i] = 0.f;
+    }
+    __syncwarp();
+  }
+}
+
+__global__ void __launch_bounds__(1024)
+moe_plan_kernel(const int* __restrict__ ids, int n_pairs, int E, int* __restrict__ offsets,
+                int* __restrict__ sorted_pair, int* __restrict__ tile_expert, int* __restrict__ tile_row0,
+                int* __restrict__ tile_rows, int* __restrict__ n_tiles, int max_tiles) {
+  extern __shared__ int ism[];
+  int* cnt = ism;      // [E]
+  int* cur = ism + E;  // [E]
+  int* off = cur + E;  // [E + 1]
+  for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = cur[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+    const int e = ids[i];
+    if (e >= 0 && e < E) atomicAdd(&cnt[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int o = 0, nt = 0;
+    for (int e = 0; e < E; ++e) {
+      off[e] = o;
+      for (int r = 0; r < cnt[e] && nt < max_tiles; r += TILE_ROWS, ++nt) {
+        tile_expert[nt] = e;
+        tile_row0[nt] = o + r;
+        tile_rows[nt] = min(TILE_ROWS, cnt[e] - r);
+      }
+      o += cnt[e];
+    }
+    off[E] = o;
+    *n_tiles = nt;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) offsets[e] = off[e];
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+    const int e = ids[i];
+    if (e >= 0 && e < E) sorted_pair[off[e] + atomicAdd(&cur[e], 1)] = i;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_product_kernel(const T* __restrict__ A, long lda, const int* __restrict__ a_rows, int a_div,
+                   const T* __restrict__ B, void* __restrict__ C, int c_dtype, long ldc,
+                   const int* __restrict__ c_rows, const int* __restrict__ tile_expert,
+                   const int* __restrict__ tile_row0, const int* __restrict__ tile_rows,
+                   const int* __restrict__ n_tiles, int N, int K, int act) {
+  const int tile = blockIdx.x;
+  if (tile >= *n_tiles) return;
+  __shared__ float As[TILE_K][TILE_ROWS + 1];
+  __shared__ float Bs[TILE_K][TILE_COLS + 1];
+  __shared__ long arow[TILE_ROWS], crow[TILE_ROWS];
+  const int e = tile_expert[tile], r0 = tile_row0[tile], nr = tile_rows[tile];
+  const int n0 = blockIdx.y * TILE_COLS;
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  if (tid < TILE_ROWS) {
+    const int i = r0 + tid;
+    arow[tid] = tid < nr ? (a_rows ? (long)(a_rows[i] / a_div) : (long)i) : -1;
+    crow[tid] = tid < nr ? (c_rows ? (long)c_rows[i] : (long)i) : -1;
+  }
+  __syncthreads();
+  const T* Be = B + (size_t)e * N * K;
+  float acc[2][4] = {};
+  for (int k0 = 0; k0 < K; k0 += TILE_K) {
+    for (int idx = tid; idx < TILE_ROWS * TILE_K; idx += 256) {
+      const int r = idx / TILE_K, k = idx % TILE_K;
+      As[k][r] = (arow[r] >= 0 && k0 + k < K) ? to_f32(A[(size_t)arow[r] * lda + k0 + k]) : 0.f;
+    }
+    for (int idx = tid; idx < TILE_COLS * TILE_K; idx += 256) {
+      const int n = idx / TILE_K, k = idx % TILE_K;
+      Bs[k][n] = (n0 + n < N && k0 + k < K) ? to_f32(Be[(size_t)(n0 + n) * K + k0 + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < TILE_K; ++k) {
+      const float a0 = As[k][ty * 2], a1 = As[k][ty * 2 + 1];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float b = Bs[k][tx * 4 + j];
+        acc[0][j] = fmaf(a0, b, acc[0][j]);
+        acc[1][j] = fmaf(a1, b, acc[1][j]);
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const long cr = crow[ty * 2 + i];
+    if (cr < 0) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n >= N) continue;
+      float v = acc[i][j];
+      if (act == 1) {
+        v = fmaxf(v, 0.f);
+        v *= v;
+      }
+      st_any(C, c_dtype, (size_t)cr * ldc + n, v);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const float* __restrict__ P, long ldp, const float* __restrict__ wts, const int* __restrict__ ids,
+                   float* __restrict__ y, long ldy, long T, int top, int width) {
+  const long n = T * width;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+    const long t = i / width;
+    const int c = (int)(i % width);
+    float acc = 0.f;
+    for (int k = 0; k < top; ++k)
+      if (ids[t * top + k] >= 0) acc = fmaf(wts[t * top + k], P[(size_t)(t * top + k) * ldp + c], acc);
+    y[(size_t)t * ldy + c] = acc;
+  }
+}
+}  // namespace
+
+extern "C" int dsp_moe_tile_rows() { return TILE_ROWS; }
+
+extern "C" int dsp_moe_route(const void* h, int h_dtype, long ldh, const float* w, int T, int W, int E, int groups,
+                             int keep, int top, int* ids, float* wts, cudaStream_t stream) {
+  if (T == 0) return 0;
+  DSP_REQUIRE(h && w && ids && wts, "dsp_moe_route: missing operand");
+  DSP_REQUIRE(E > 0 && groups > 0 && E % groups == 0 && keep > 0 && keep <= groups && top > 0 &&
+                  top <= keep * (E / groups),
+              "dsp_moe_route: experts=%d groups=%d keep=%d top=%d do not fit together", E, groups, keep, top);
+  const int warps = 4;
+  const size_t smem = (size_t)warps * (2 * E + groups) * sizeof(float);
+  DSP_REQUIRE(smem <= 48 * 1024, "dsp_moe_route: %d experts are more than the router kernel holds", E);
+  DSP_CUDA(launch_plain(moe_route_kernel, dim3((unsigned)((T + warps - 1) / warps)), dim3(32 * warps), smem, stream, h,
+                        h_dtype, ldh, w, T, W, E, groups, keep, top, ids, wts));
+  DSP_CHECK_LAUNCH("dsp_moe_route");
+  return 0;
+}
+
+extern "C" int dsp_moe_plan(const int* ids, int n_pairs, int E, int* offsets, int* sorted_pair, int* tile_expert,
+                            int* tile_row0, int* tile_rows, int* n_tiles, int max_tiles, cudaStream_t stream) {
+  DSP_REQUIRE(ids && offsets && sorted_pair && tile_expert && tile_row0 && tile_rows && n_tiles, "dsp_moe_plan: missing operand");
+  DSP_REQUIRE(max_tiles >= n_pairs / TILE_ROWS + E, "dsp_moe_plan: room for %d tiles, %d may be needed", max_tiles,
+              n_pairs / TILE_ROWS + E);
+  const size_t smem = (size_t)(3 * E + 1) * sizeof(int);
+  DSP_REQUIRE(smem <= 48 * 1024, "dsp_moe_plan: %d experts are more than the planning kernel holds", E);
+  DSP_CUDA(launch_plain(moe_plan_kernel, dim3(1), dim3(1024), smem, stream, ids, n_pairs, E, offsets, sorted_pair,
+                        tile_expert, tile_row0, tile_rows, n_tiles, max_tiles));
+  DSP_CHECK_LAUNCH("dsp_moe_plan");
+  return 0;
+}
+
+extern "C" int dsp_moe_product(const void* A, int ab_dtype, long lda, const int* a_rows, int a_div, const void* B,
+                               void* C, int c_dtype, long ldc, const int* c_rows, const int* tile_expert,
+                               const int* tile_row0, const int* tile_rows, const int* n_tiles, int max_tiles, int N,
+                               int K, int act, cudaStream_t stream) {
+  if (max_tiles == 0 || N == 0) return 0;
+  DSP_REQUIRE(A && B && C && tile_expert && tile_row0 && tile_rows && n_tiles && a_div > 0, "dsp_moe_product: missing operand");
+  DSP_REQUIRE(act == 0 || act == 1, "dsp_moe_product: unknown activation %d", act);
+  dim3 grid(max_tiles, (N + TILE_COLS - 1) / TILE_COLS);
+  DSP_REQUIRE(grid.y <= 65535, "dsp_moe_product: N=%d is too wide", N);
+  if (ab_dtype == DSP_F32) {
+    DSP_CUDA(launch_plain(moe_product_kernel<float>, grid, dim3(256), 0, stream, (const float*)A, lda, a_rows, a_div,
+                          (const float*)B, C, c_dtype, ldc, c_rows, tile_expert, tile_row0, tile_rows, n_tiles, N, K, act));
+  } else {
+    DSP_CUDA(launch_plain(moe_product_kernel<bf16>, grid, dim3(256), 0, stream, (const bf16*)A, lda, a_rows, a_div,
+                          (const bf16*)B, C, c_dtype, ldc, c_rows, tile_expert, tile_row0, tile_rows, n_tiles, N, K, act));
+  }
+  DSP_CHECK_LAUNCH("dsp_moe_product");
+  return 0;
+}
+
+extern "C" int dsp_moe_combine(const float* P, long ldp, const float* wts, const int* ids, float* y, long ldy, long T,
+                               int top, int width, cudaStream_t stream) {
+  if (T == 0) return 0;
+  DSP_REQUIRE(P && wts && ids && y, "dsp_moe_combine: missing operand");
+  const long n = T * width;
+  const int sms = dsp_num_sms();
+  const long want = (n + 255) / 256, cap = (long)(sms > 0 ? sms : 148) * 16;
+  DSP_CUDA(launch_plain(moe_combine_kernel, dim3((unsigned)(want < cap ? want : cap)), dim3(256), 0, stream, P, ldp,
+                        wts, ids, y, ldy, T, top, width));
+  DSP_CHECK_LAUNCH("dsp_moe_combine");
+  return 0;
+}

@@ -35,26 +35,30 @@ def tcgen05_supported(head_dim: int, group_size: int, page_size: int, dtype: tor
 def paged_attention_generic(q: torch.Tensor, q_stride: int, k_pool: torch.Tensor, v_pool: torch.Tensor,
                             page_table: torch.Tensor, positions: torch.Tensor,
                             seq_of_token: torch.Tensor, out: torch.Tensor, num_heads: int,
-                            num_kv_heads: int, head_dim: int, window: int, scale: float) -> torch.Tensor:
-    """32-bit arithmetic kernel, any head size up to 512 and any group size.
+                            num_kv_heads: int, head_dim: int, window: int, scale: float,
+                            sink: bool = False) -> torch.Tensor:
+    """32-bit arithmetic kernel, any value size up to 512 and any group size.
 
-    q: element (t, h, d) at q.data_ptr + (t * q_stride + h * D + d); out: [T, H * D].
+    q: element (t, h, d) at q.data_ptr + (t * q_stride + h * D + d); out: [T, H * Dv], Dv being the
+    width of the value pool (it may differ from the keys' D).
     The query at absolute position p = positions[t] sees keys max(0, p-window+1)..p
-    (window 0: from 0) of sequence seq_of_token[t].
+    (window 0: from 0) of sequence seq_of_token[t].  ``sink``: the softmax has one more key of
+    score 0 and no value (weights exp(s_j) / (1 + sum exp(s_j))).
     """
     assert q.is_cuda and k_pool.is_cuda, "CUDA tensors only (there is no CPU path)"
     T = positions.shape[0]
     num_pages, kvh, page_size, d = k_pool.shape
-    assert (kvh, d) == (num_kv_heads, head_dim) and v_pool.shape == k_pool.shape
-    assert k_pool.is_contiguous() and v_pool.is_contiguous() and k_pool.dtype == q.dtype
-    assert out.is_contiguous() and out.shape == (T, num_heads * head_dim) and out.dtype == q.dtype
+    dv = v_pool.shape[3]
+    assert (kvh, d) == (num_kv_heads, head_dim) and v_pool.shape[:3] == k_pool.shape[:3]
+    assert k_pool.is_contiguous() and v_pool.is_contiguous() and k_pool.dtype == q.dtype == v_pool.dtype
+    assert out.is_contiguous() and out.shape == (T, num_heads * dv) and out.dtype == q.dtype
     assert page_table.dtype == torch.int32 and page_table.stride(1) == 1
     assert positions.dtype == torch.int32 and seq_of_token.dtype == torch.int32
     L.check(L.core().dsp_attn_generic(
         L.ptr(q), L.i64(q_stride), L.ptr(k_pool), L.ptr(v_pool), L.ptr(page_table),
         page_table.stride(0), L.ptr(positions), L.ptr(seq_of_token), L.ptr(out),
-        L.i64(out.stride(0)), T, num_heads, num_kv_heads, head_dim, page_size, num_pages,
-        window, L.f32(scale), L.dtype_code(q.dtype), L.stream_handle()))
+        L.i64(out.stride(0)), T, num_heads, num_kv_heads, head_dim, dv, page_size, num_pages,
+        window, L.f32(scale), int(sink), L.dtype_code(q.dtype), L.stream_handle()))
     return out
 
 
@@ -287,3 +291,56 @@ def paged_attention(ctx, q: torch.Tensor, q_stride: int, cache, out: torch.Tenso
     return paged_attention_generic(q, q_stride, cache.key_pool, cache.value_pool, cache.page_table,
                                    ctx.positions, ctx.seq_of_token, out, num_heads, num_kv_heads,
                                    head_dim, window, scale)
+
+
+def qkv_rotate_store(qkv: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor, cache,
+                     inv_freq: torch.Tensor | None, rotary_dim: int, num_heads: int, num_kv_heads: int,
+                     key_dim: int, value_dim: int, out_dtype: torch.dtype, v_other: torch.Tensor | None = None,
+                     blend: torch.Tensor | None = None) -> torch.Tensor:
+    """From rows [q (H x Dk) | k (G x Dk) | v (G x Dv)] of a fused projection: turns pairs
+    (i, i + rotary_dim/2) of every query and key head by position * inv_freq[i] in 32-bit, blends
+    v <- (1 - blend) v + blend * v_other when ``v_other`` [T, G * Dv] is given (``blend``: a float32
+    scalar on the device), stores key and value into the pages of ``cache`` (its "key" and "value"
+    pools, of widths Dk and Dv) when the cache is written by this call, and returns the turned
+    queries [T, H * Dk] in ``out_dtype``.  Rows with a negative position are skipped."""
+    if not qkv.is_cuda:
+        raise L.KernelError("qkv_rotate_store: CUDA tensors only (there is no CPU path)")
+    T = qkv.shape[0]
+    H, G, dk, dv = num_heads, num_kv_heads, key_dim, value_dim
+    assert qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] == (H + G) * dk + G * dv
+    k_pool, v_pool = cache.key_pool, cache.value_pool
+    num_pages, g_, page_size, dk_ = k_pool.shape
+    assert (g_, dk_) == (G, dk) and v_pool.shape == (num_pages, G, page_size, dv)
+    assert k_pool.is_contiguous() and v_pool.is_contiguous() and k_pool.dtype == v_pool.dtype == out_dtype
+    table = cache.page_table
+    assert table.dtype == torch.int32 and table.stride(1) == 1
+    if rotary_dim:
+        assert inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.shape[0] >= rotary_dim // 2
+    if v_other is not None:
+        assert blend is not None and blend.dtype == torch.float32 and blend.numel() == 1 and blend.is_cuda
+        assert v_other.shape == (T, G * dv) and v_other.stride(1) == 1
+    q_out = torch.empty((T, H * dk), dtype=out_dtype, device=qkv.device)
+    lib = L.mixer_library("attn_sink")
+    L.check(lib.dsp_qkv_rotate_store(
+        L.ptr(qkv), L.dtype_code(qkv.dtype), L.i64(qkv.stride(0)), L.ptr(positions), L.ptr(seq_of_token),
+        L.ptr(table), table.stride(0), L.ptr(k_pool), L.ptr(v_pool), L.dtype_code(out_dtype), L.ptr(inv_freq),
+        rotary_dim, L.ptr(v_other), L.dtype_code(v_other.dtype) if v_other is not None else 0,
+        L.i64(v_other.stride(0) if v_other is not None else 0), L.ptr(blend if v_other is not None else None),
+        L.ptr(q_out), L.i64(q_out.stride(0)), T, H, G, dk, dv, page_size, num_pages, int(cache.write),
+        L.stream_handle()))
+    return q_out
+
+
+def sink_tokens_per_tile(group_size: int, key_dim: int, value_dim: int):
+    """Query tokens per tile that the tensor-core kernel of ``sink_paged_attention`` wants listed
+    in the batch (None: the 32-bit kernel runs, which needs no tile list)."""
+    return None
+
+
+def sink_paged_attention(ctx, q: torch.Tensor, cache, out: torch.Tensor, num_heads: int, num_kv_heads: int,
+                         key_dim: int, value_dim: int, window: int, scale: float, sink: bool) -> torch.Tensor:
+    """Attention of the step over pools whose keys and values have widths of their own, with an
+    optional sink in the softmax: q [T, H * Dk] (already turned), out [T, H * Dv]."""
+    return paged_attention_generic(q, q.stride(0), cache.key_pool, cache.value_pool, cache.page_table,
+                                   ctx.positions, ctx.seq_of_token, out, num_heads, num_kv_heads, key_dim,
+                                   window, scale, sink=sink)

@@ -1,0 +1,86 @@
+"""Mixture of experts on the device: router with groups, rows sorted by expert, the experts'
+products, the weighted sum.  See ``csrc/moe.cu``."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from dispec_b200.ops import library as L
+
+
+def _lib():
+    return L.mixer_library("moe")
+
+
+def route(h: torch.Tensor, w_router: torch.Tensor, groups: int, keep: int, top: int):
+    """h [T, W] (either type), w_router float32 [E, W] -> (ids int32 [T, top], weights float32
+    [T, top]): softmax over all experts in 32-bit; the ``top`` largest scores among the experts
+    of the ``keep`` groups (of ``groups`` equal runs of neighbours) with the largest best score;
+    the weights are those scores."""
+    if not (h.is_cuda and w_router.is_cuda):
+        raise L.KernelError("moe.route: CUDA tensors only (there is no CPU path)")
+    assert h.dim() == 2 and h.stride(1) == 1 and w_router.dtype == torch.float32 and w_router.is_contiguous()
+    T, W = h.shape
+    E = w_router.shape[0]
+    assert w_router.shape == (E, W)
+    ids = torch.empty((T, top), dtype=torch.int32, device=h.device)
+    wts = torch.empty((T, top), dtype=torch.float32, device=h.device)
+    L.check(_lib().dsp_moe_route(L.ptr(h), L.dtype_code(h.dtype), L.i64(h.stride(0)), L.ptr(w_router), T, W, E,
+                                 groups, keep, top, L.ptr(ids), L.ptr(wts), L.stream_handle()))
+    return ids, wts
+
+
+@dataclass
+class ExpertPlan:
+    """The (token, choice) pairs of a step listed expert by expert, cut into tiles."""
+    sorted_pair: torch.Tensor  # [pairs] int32: pair index t * top + k at each sorted place
+    offsets: torch.Tensor  # [E + 1] int32
+    tiles: torch.Tensor  # [3, max_tiles] int32: expert, first sorted row, rows
+    n_tiles: torch.Tensor  # [1] int32
+    max_tiles: int
+    num_pairs: int
+    top: int
+
+
+def plan(ids: torch.Tensor, num_experts: int) -> ExpertPlan:
+    T, top = ids.shape
+    n = T * top
+    lib = _lib()
+    max_tiles = n // int(lib.dsp_moe_tile_rows()) + num_experts
+    dev = ids.device
+    sorted_pair = torch.empty(max(n, 1), dtype=torch.int32, device=dev)
+    offsets = torch.empty(num_experts + 1, dtype=torch.int32, device=dev)
+    tiles = torch.empty((3, max_tiles), dtype=torch.int32, device=dev)
+    n_tiles = torch.empty(1, dtype=torch.int32, device=dev)
+    L.check(lib.dsp_moe_plan(L.ptr(ids), n, num_experts, L.ptr(offsets), L.ptr(sorted_pair), L.ptr(tiles[0]),
+                             L.ptr(tiles[1]), L.ptr(tiles[2]), L.ptr(n_tiles), max_tiles, L.stream_handle()))
+    return ExpertPlan(sorted_pair, offsets, tiles, n_tiles, max_tiles, n, top)
+
+
+def expert_product(p: ExpertPlan, a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, *,
+                   rows_are_tokens: bool, scatter: bool, square_relu: bool = False) -> torch.Tensor:
+    """C = act(A W_e^T) for every pair, with its expert's matrix (w: [E, N, K]).  ``rows_are_tokens``:
+    A holds one row per token (a pair reads its token's row); otherwise one row per sorted place.
+    ``scatter``: the result row of a pair goes to its pair index t * top + k; otherwise to its
+    sorted place.  Returns [pairs, N]."""
+    assert a.dim() == 2 and a.stride(1) == 1 and w.dim() == 3 and w.is_contiguous() and a.dtype == w.dtype
+    E, N, K = w.shape
+    assert a.shape[1] == K
+    out = torch.empty((max(p.num_pairs, 1), N), dtype=out_dtype, device=a.device)
+    L.check(_lib().dsp_moe_product(
+        L.ptr(a), L.dtype_code(a.dtype), L.i64(a.stride(0)), L.ptr(p.sorted_pair if rows_are_tokens else None),
+        p.top if rows_are_tokens else 1, L.ptr(w), L.ptr(out), L.dtype_code(out_dtype), L.i64(out.stride(0)),
+        L.ptr(p.sorted_pair if scatter else None), L.ptr(p.tiles[0]), L.ptr(p.tiles[1]), L.ptr(p.tiles[2]),
+        L.ptr(p.n_tiles), p.max_tiles, N, K, int(square_relu), L.stream_handle()))
+    return out[:p.num_pairs]
+
+
+def combine(pair_rows: torch.Tensor, wts: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+    """y[t] = sum over k of wts[t, k] * pair_rows[t * top + k] (float32)."""
+    T, top = ids.shape
+    assert pair_rows.dtype == torch.float32 and pair_rows.stride(1) == 1 and pair_rows.shape[0] == T * top
+    y = torch.empty((T, pair_rows.shape[1]), dtype=torch.float32, device=pair_rows.device)
+    L.check(_lib().dsp_moe_combine(L.ptr(pair_rows), L.i64(pair_rows.stride(0)), L.ptr(wts), L.ptr(ids), L.ptr(y),
+                                   L.i64(y.stride(0)), L.i64(T), top, pair_rows.shape[1], L.stream_handle()))
+    return y

@@ -47,9 +47,11 @@ def sum_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, delta: torch.Ten
 
 
 def head_norm_gate(o: torch.Tensor, num_heads: int, eps: float, out_dtype: torch.dtype,
-                   gain: torch.Tensor | None = None, gate: torch.Tensor | None = None) -> torch.Tensor:
+                   gain: torch.Tensor | None = None, gate: torch.Tensor | None = None,
+                   gate_kind: str = "silu") -> torch.Tensor:
     """o float32 [T, H * dv]: every head's dv values divided by their root mean square (eps inside
-    the root), times ``gain`` [dv] (optional) and silu(gate[t, h * dv + j]) (optional)."""
+    the root), times ``gain`` [dv] (optional) and act(gate[t, h * dv + j]) (optional; ``gate_kind``
+    "silu" or "sigmoid").  With ``num_heads`` 1 the whole row is normed together."""
     _rows2d(o, "head_norm_gate")
     assert o.dtype == torch.float32 and o.shape[1] % num_heads == 0
     T, dv = o.shape[0], o.shape[1] // num_heads
@@ -62,7 +64,7 @@ def head_norm_gate(o: torch.Tensor, num_heads: int, eps: float, out_dtype: torch
     L.check(L.core().dsp_head_norm_gate(
         L.ptr(o), L.i64(o.stride(0)), L.ptr(gain), L.ptr(gate), L.dtype_code(gate.dtype) if gate is not None else 0,
         L.i64(gate.stride(0) if gate is not None else 0), L.ptr(y), L.dtype_code(out_dtype), L.i64(y.stride(0)),
-        T, num_heads, dv, L.f32(eps), L.stream_handle()))
+        T, num_heads, dv, L.f32(eps), {"silu": 0, "sigmoid": 1}[gate_kind], L.stream_handle()))
     return y
 
 
@@ -76,3 +78,95 @@ def xielu(z: torch.Tensor, params: torch.Tensor, out_dtype: torch.dtype) -> torc
                                L.dtype_code(out_dtype), L.i64(y.stride(0)), L.i64(z.shape[0]), z.shape[1],
                                L.stream_handle()))
     return y
+
+
+def layer_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
+               rows: torch.Tensor | None = None) -> torch.Tensor:
+    """y = (x - mean) / sqrt(var + eps) * weight per row (var: the mean of the squared deviations),
+    in 32-bit, written as ``out_dtype``.  ``rows`` (int32) gathers input rows."""
+    _rows2d(x, "layer_norm")
+    assert weight.dtype == torch.float32 and weight.is_contiguous() and weight.shape == (x.shape[1],)
+    if rows is not None:
+        assert rows.dtype == torch.int32 and rows.is_contiguous()
+    n = x.shape[0] if rows is None else rows.shape[0]
+    y = torch.empty((n, x.shape[1]), dtype=out_dtype, device=x.device)
+    L.check(L.core().dsp_layer_norm(L.ptr(x), L.dtype_code(x.dtype), L.i64(x.stride(0)), L.ptr(weight), L.f32(eps),
+                                    L.ptr(rows), L.ptr(y), L.dtype_code(out_dtype), L.i64(y.stride(0)), n, x.shape[1],
+                                    L.stream_handle()))
+    return y
+
+
+def stream_update(x32: torch.Tensor, y: torch.Tensor, *, gate: torch.Tensor | None = None,
+                  scale: torch.Tensor | None = None, rms_weight: torch.Tensor | None = None, rms_eps: float = 0.0,
+                  norm_weight: torch.Tensor | None = None, norm_eps: float = 0.0,
+                  out_dtype: torch.dtype | None = None) -> torch.Tensor | None:
+    """x32 += d in place (float32 rows), with d = y * scale * sigmoid(gate) when ``gate`` is given,
+    d = y / sqrt(mean(y^2) + rms_eps) * rms_weight when ``rms_weight`` is, else d = y.  With
+    ``out_dtype``: also returns the layer norm of the new rows times ``norm_weight`` (or, without
+    ``norm_weight``, the new rows themselves) in that type."""
+    _rows2d(x32, "stream_update")
+    _rows2d(y, "stream_update")
+    assert x32.dtype == torch.float32 and y.shape == x32.shape
+    width = x32.shape[1]
+    for v in (scale, rms_weight, norm_weight):
+        assert v is None or (v.dtype == torch.float32 and v.is_contiguous() and v.shape == (width,))
+    if gate is not None:
+        _rows2d(gate, "stream_update")
+        assert gate.shape == x32.shape
+    out = torch.empty(x32.shape, dtype=out_dtype, device=x32.device) if out_dtype is not None else None
+    L.check(L.core().dsp_stream_update(
+        L.ptr(x32), L.i64(x32.stride(0)), L.ptr(y), L.dtype_code(y.dtype), L.i64(y.stride(0)), L.ptr(gate),
+        L.dtype_code(gate.dtype) if gate is not None else 0, L.i64(gate.stride(0) if gate is not None else 0),
+        L.ptr(scale), L.ptr(rms_weight), L.f32(rms_eps), L.ptr(norm_weight), L.f32(norm_eps), L.ptr(out),
+        L.dtype_code(out_dtype) if out is not None else 0, L.i64(out.stride(0) if out is not None else 0),
+        x32.shape[0], width, L.stream_handle()))
+    return out
+
+
+def clamped_glu(z: torch.Tensor, limit: float, alpha: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """z [T, 2 n] = [gates | ups] -> [T, n]: g = min(gate, limit), u = clamp(up, -limit, limit),
+    g * sigmoid(alpha * g) * (u + 1)."""
+    _rows2d(z, "clamped_glu")
+    assert z.shape[1] % 2 == 0
+    n = z.shape[1] // 2
+    y = torch.empty((z.shape[0], n), dtype=out_dtype, device=z.device)
+    L.check(L.core().dsp_clamped_glu(L.ptr(z), L.dtype_code(z.dtype), L.i64(z.stride(0)), L.ptr(y),
+                                     L.dtype_code(out_dtype), L.i64(y.stride(0)), L.i64(z.shape[0]), n, L.f32(limit),
+                                     L.f32(alpha), L.stream_handle()))
+    return y
+
+
+def gelu_table_gate(z: torch.Tensor, table: torch.Tensor, offset: int, ids: torch.Tensor,
+                    out_dtype: torch.dtype) -> torch.Tensor:
+    """y[t, j] = gelu_tanh(z[t, j]) * table[ids[t], offset + j]."""
+    _rows2d(z, "gelu_table_gate")
+    _rows2d(table, "gelu_table_gate")
+    assert ids.dtype == torch.int32 and ids.is_contiguous() and ids.shape[0] >= z.shape[0]
+    assert 0 <= offset and offset + z.shape[1] <= table.shape[1]
+    y = torch.empty(z.shape, dtype=out_dtype, device=z.device)
+    L.check(L.core().dsp_gelu_table_gate(
+        L.ptr(z), L.dtype_code(z.dtype), L.i64(z.stride(0)), L.ptr(table), L.dtype_code(table.dtype),
+        L.i64(table.stride(0)), table.shape[0], offset, L.ptr(ids), L.ptr(y), L.dtype_code(out_dtype),
+        L.i64(y.stride(0)), L.i64(z.shape[0]), z.shape[1], L.stream_handle()))
+    return y
+
+
+def softcap_(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """x <- cap * tanh(x / cap) in place (float32 rows)."""
+    _rows2d(x, "softcap")
+    assert x.dtype == torch.float32
+    L.check(L.core().dsp_softcap(L.ptr(x), L.i64(x.stride(0)), L.i64(x.shape[0]), x.shape[1], L.f32(cap),
+                                 L.stream_handle()))
+    return x
+
+
+def embed_scaled(table: torch.Tensor, ids: torch.Tensor, scale: float) -> torch.Tensor:
+    """float32 rows table[ids[t]] * scale (a token id outside the table gives zeros and sets the
+    device error word)."""
+    _rows2d(table, "embed_scaled")
+    assert table.is_contiguous() and ids.dtype == torch.int32 and ids.is_contiguous()
+    out = torch.empty((ids.shape[0], table.shape[1]), dtype=torch.float32, device=table.device)
+    L.check(L.core().dsp_embed_scaled(L.ptr(table), L.dtype_code(table.dtype), table.shape[0], L.ptr(ids),
+                                      L.f32(scale), L.ptr(out), L.i64(out.stride(0)), L.i64(ids.shape[0]),
+                                      table.shape[1], L.stream_handle()))
+    return out

@@ -13,12 +13,14 @@ def linear_recurrence(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, mo
                       dim: int, vdim: int, state: torch.Tensor, state_slot: torch.Tensor,
                       q_start: torch.Tensor, positions: torch.Tensor, *, decay: torch.Tensor | None = None,
                       inv_freq: torch.Tensor | None = None, rot: int = 0, key_scale: float = 1.0,
-                      gate_bias: torch.Tensor | None = None, lower: torch.Tensor | None = None) -> torch.Tensor:
+                      gate_bias: torch.Tensor | None = None, lower: torch.Tensor | None = None,
+                      silu_inputs: bool = False) -> torch.Tensor:
     """``proj`` [T, columns]: the raw rows of the mixer's fused projection (query columns from
     ``q_off``, key or forget-gate columns from ``k_off``, value columns from ``v_off``, each head by
     head).  ``state`` float32 [slots, H, dim, vdim] is read and left updated for the sequences of the
     step (``q_start`` [S + 1], ``state_slot`` [S]); a sequence whose first position is negative is
-    skipped.  Returns o as float32 [T, H * vdim]."""
+    skipped.  ``silu_inputs`` (fixed decay only): the raw query, key and value columns pass through
+    silu before anything else.  Returns o as float32 [T, H * vdim]."""
     if not (proj.is_cuda and state.is_cuda):
         raise L.KernelError("linear_recurrence: CUDA tensors only (there is no CPU path)")
     assert proj.dim() == 2 and proj.stride(1) == 1
@@ -40,7 +42,7 @@ def linear_recurrence(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, mo
         scratch = torch.empty((T, planes, num_heads * dim), dtype=torch.float32, device=proj.device)
     L.check(lib.dsp_linear_recurrence(
         L.ptr(proj), L.dtype_code(proj.dtype), L.i64(proj.stride(0)), q_off, k_off, v_off, mode, num_heads, dim,
-        vdim, L.ptr(decay), L.ptr(inv_freq), rot, L.f32(key_scale), L.ptr(gate_bias), L.ptr(lower), L.ptr(state),
+        vdim, L.ptr(decay), L.ptr(inv_freq), rot, L.f32(key_scale), int(silu_inputs), L.ptr(gate_bias), L.ptr(lower), L.ptr(state),
         L.ptr(state_slot), L.ptr(q_start), L.ptr(positions), L.ptr(out), L.i64(out.stride(0)), S, T,
         L.ptr(scratch), L.stream_handle()))
     return out

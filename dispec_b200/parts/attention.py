@@ -1,4 +1,6 @@
-"""Grouped-query attention over the paged cache.
+"""Grouped-query attention over the paged cache: ``gqa_attention`` (keys and values of one
+width, plain softmax) and ``sink_attention`` (widths of their own, an optional sink in the
+softmax, values optionally blended with another layer's; at the end of this file).
 
 q, k, v = h W^T + b (one fused product, rows ordered q, k, v: puneethgv/DiSpec
 dispec/engine/model_runner.py:104-118,131-136); rotation of q and k and the write of k, v
@@ -13,6 +15,7 @@ import torch
 
 from dispec_b200 import ops
 from dispec_b200.ops import attention as attn_ops
+from dispec_b200.cache.manager import CacheTensor
 from dispec_b200.parts.base import CacheNeed, Mixer, TensorSpec
 from dispec_b200.registry import register_part
 
@@ -102,3 +105,81 @@ class GQAAttention(Mixer):
         attn_ops.paged_attention(ctx, qkv, qkv.stride(0), cache, out, H, KVH, D, self.window,
                                  scale, fused_rope=fused)
         return ops.linear(out, self.w_o, self.b_o, residual=residual, out=residual, then_norm=then_norm)
+
+
+@register_part("mixer", "sink_attention")
+class SinkAttention(Mixer):
+    """Grouped-query attention whose keys (``key_dim``) and values (``value_dim``) have widths of
+    their own:
+
+        q = W_q h, k = W_k h, v = W_v h (no biases); q and k turned by the position encoding;
+        s_j = (q . k_j) * scale over the keys j the window lets position p see (p - window < j <= p;
+        window 0: every j <= p);
+        sink:     weights exp(s_j) / (1 + sum_j exp(s_j))   (one more key of score 0 and no value)
+        no sink:  the plain softmax;
+        output projection W_o on the concatenated heads.
+
+    ``value_mix``: None, or a pair (role, key).  The mixer with role "source" publishes its values
+    of the step's tokens under ``key``; one with role "blend" replaces its own by
+    (1 - m) v + m v_source, m being its tensor ``value_mix`` (a scalar), before they are cached and
+    used.  A source owns the tensor too (unused), so that checkpoints list it for every such layer.
+    Scores, softmax, angles and the blend are 32-bit; the projections return 32-bit rows, which
+    are rounded once, after the rotation and the blend, when they enter the cache."""
+
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int,
+                 scale: float, position_encoding, window: int = 0, sink: bool = True, value_mix=None):
+        if num_heads % num_kv_heads:
+            raise ValueError(f"num_heads={num_heads} is not a multiple of num_kv_heads={num_kv_heads}")
+        if not float(scale) > 0.0:
+            raise ValueError(f"the attention scale must be positive, got {scale}")
+        if value_mix is not None and (len(value_mix) != 2 or value_mix[0] not in ("source", "blend")):
+            raise ValueError(f"value_mix must be None or ('source' | 'blend', key), got {value_mix!r}")
+        self.hidden_size, self.num_heads, self.num_kv_heads = hidden_size, num_heads, num_kv_heads
+        self.key_dim, self.value_dim = key_dim, value_dim
+        self.scale, self.window, self.sink = float(scale), int(window), bool(sink)
+        self.position_encoding = position_encoding
+        self.value_mix = tuple(value_mix) if value_mix is not None else None
+        self.w_qkv = self.w_o = self.blend = None
+
+    def tensor_specs(self):
+        h, H, G, dk, dv = self.hidden_size, self.num_heads, self.num_kv_heads, self.key_dim, self.value_dim
+        specs = {"q.weight": TensorSpec((H * dk, h)), "k.weight": TensorSpec((G * dk, h)),
+                 "v.weight": TensorSpec((G * dv, h)), "o.weight": TensorSpec((h, H * dv))}
+        if self.value_mix is not None:
+            specs["value_mix"] = TensorSpec((), dtype="float32")
+        return specs
+
+    def load(self, tensors):
+        self.w_qkv = torch.cat([tensors["q.weight"], tensors["k.weight"], tensors["v.weight"]], dim=0).contiguous()
+        self.w_o = tensors["o.weight"]
+        self.blend = tensors.get("value_mix")
+
+    def cache_need(self):
+        return CacheNeed((CacheTensor("key", self.num_kv_heads, self.key_dim),
+                          CacheTensor("value", self.num_kv_heads, self.value_dim)), self.window)
+
+    def tokens_per_attention_tile(self):
+        return attn_ops.sink_tokens_per_tile(self.num_heads // self.num_kv_heads, self.key_dim, self.value_dim)
+
+    def forward(self, ctx, x, cache, state):
+        H, G, dk, dv = self.num_heads, self.num_kv_heads, self.key_dim, self.value_dim
+        qkv = ops.linear(x, self.w_qkv, out_dtype=torch.float32)
+        rot = self.position_encoding.rotation()
+        if rot is not None and rot.layout != "halves":
+            raise ValueError(f"sink_attention turns pairs (i, i + rotary_dim/2) only, not the {rot.layout!r} layout")
+        inv_freq, rotary_dim = (rot.inv_freq, rot.rotary_dim) if rot is not None else (None, 0)
+        v_other = None
+        if self.value_mix is not None:
+            role, key = self.value_mix
+            if role == "source":
+                ctx.scratch[("value_mix", key)] = qkv[:, (H + G) * dk:]
+            else:
+                v_other = ctx.scratch.get(("value_mix", key))
+                if v_other is None:
+                    raise ValueError(f"sink_attention: no layer published the values {key!r} before this one")
+        q = attn_ops.qkv_rotate_store(qkv, ctx.positions, ctx.seq_of_token, cache, inv_freq, rotary_dim, H, G, dk, dv,
+                                      ctx.dtype, v_other=v_other, blend=self.blend)
+        out = torch.empty((q.shape[0], H * dv), dtype=q.dtype, device=q.device)
+        attn_ops.sink_paged_attention(ctx, q, cache, out, H, G, dk, dv, self.window,
+                                      self.scale * self.position_encoding.score_scale(), self.sink)
+        return ops.linear(out, self.w_o, out_dtype=torch.float32)

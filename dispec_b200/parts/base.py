@@ -81,11 +81,12 @@ class StateNeed:
 @dataclass
 class WideStream:
     """A residual stream kept in 32-bit floats (``full``, [T, width]) beside the copy rounded to
-    the model type that the products read (``rounded``; the same tensor on the 32-bit path).
+    the model type that the products read (``rounded``; the same tensor on the 32-bit path; None
+    where the arrangement reads the stream through a norm only and keeps no such copy).
     Blocks that keep the stream this way pass it on as their ``x``; a norm that takes it
     (``rms_norm_f32``) reads ``full``."""
     full: torch.Tensor
-    rounded: torch.Tensor
+    rounded: torch.Tensor | None
 
     @property
     def shape(self):

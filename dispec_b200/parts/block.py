@@ -1,4 +1,4 @@
-"""Arrangement of a layer: pre-norm residual block.
+"""Arrangements of a layer.  The pre-norm residual block:
 
     x += pending;  h = norm1(x);  a = mixer(h);  x += a;  h = norm2(x);  pending = ffn(h)
 
@@ -8,8 +8,12 @@ feed-forward output on as ``pending`` so that the next block's first norm (or th
 adds it."""
 from __future__ import annotations
 
+import torch
+
 from dispec_b200.ops.gemm import NormedRows
-from dispec_b200.parts.base import Block, WideStream
+from dispec_b200 import ops
+from dispec_b200.ops import norm32 as norm32_ops
+from dispec_b200.parts.base import Block, TensorSpec, WideStream
 from dispec_b200.registry import register_part
 
 
@@ -101,3 +105,69 @@ class PostNormBlock(Block):
         if self.feed_forward is not None:
             x = self.ffn_norm.scaled_sum(ctx, x, self.feed_forward.forward(ctx, x.rounded), self.alpha)
         return x, None
+
+
+@register_part("block", "gated_pre_norm")
+class GatedPreNormBlock(Block):
+    """Pre-norm sublayers whose results are scaled per channel and gated before the sum, on a
+    residual stream kept in 32-bit floats (``WideStream``):
+
+        h = norm1(x);  x <- x + scale1 * sigmoid(G1 h + b1) * mixer(h)
+        h = norm2(x);  x <- x + scale2 * sigmoid(G2 h + b2) * ffn(h)          (if there is one)
+        x <- x + rms_norm(token_input(x)) * gain                              (if there is one)
+
+    ``token_input``: a part whose ``forward(ctx, x)`` gives a per-token addend from the stream
+    (rounded to the model type) and the step's token ids, and whose ``norm_weight`` / ``eps`` say
+    how the addend is RMS-normed before the sum.  The norms are given as parts (any norm with a
+    float32 ``weight`` and ``eps`` whose ``forward`` reads a ``WideStream``); every sum and the
+    norm that follows it run as one kernel.  The block hands the next block's first norm of its
+    result on as ``pending`` when that block is of this kind too."""
+
+    def __init__(self, hidden_size: int, mixer_norm, mixer, ffn_norm=None, feed_forward=None, token_input=None):
+        if (ffn_norm is None) != (feed_forward is None):
+            raise ValueError("gated_pre_norm: a feed-forward and its norm come together or not at all")
+        self.hidden_size = hidden_size
+        self.mixer_norm, self.mixer = mixer_norm, mixer
+        self.ffn_norm, self.feed_forward = ffn_norm, feed_forward
+        self.token_input = token_input
+
+    def tensor_specs(self):
+        h = self.hidden_size
+        specs = {}
+        for n in ("1", "2") if self.feed_forward is not None else ("1",):
+            specs["scale" + n] = TensorSpec((h,), dtype="float32", init="one_plus_normal")
+            specs["gate" + n + ".weight"] = TensorSpec((h, h))
+            specs["gate" + n + ".bias"] = TensorSpec((h,), init="zeros")
+        return specs
+
+    def load(self, tensors):
+        self.t = dict(tensors)
+
+    def first_norm_after_product(self):
+        return self.mixer_norm.weight, self.mixer_norm.eps
+
+    def _gate(self, h, n):
+        return ops.linear(h, self.t[f"gate{n}.weight"], self.t[f"gate{n}.bias"], out_dtype=torch.float32)
+
+    def forward(self, ctx, x, pending, cache, state, then_norm=None):
+        if not isinstance(x, WideStream) or x.full.dtype != torch.float32:
+            raise ValueError("gated_pre_norm: the residual stream must be a 32-bit WideStream")
+        full = x.full
+        h = pending if pending is not None else self.mixer_norm.forward(ctx, x)
+        addend = dict(y=self.mixer.forward(ctx, h, cache, state), gate=self._gate(h, 1), scale=self.t["scale1"])
+        if self.feed_forward is not None:
+            h = norm32_ops.stream_update(full, addend["y"], gate=addend["gate"], scale=addend["scale"],
+                                         norm_weight=self.ffn_norm.weight, norm_eps=self.ffn_norm.eps,
+                                         out_dtype=ctx.dtype)
+            addend = dict(y=self.feed_forward.forward(ctx, h), gate=self._gate(h, 2), scale=self.t["scale2"])
+        nw, ne = then_norm if then_norm is not None else (None, 0.0)
+        if self.token_input is None:
+            nxt = norm32_ops.stream_update(full, addend["y"], gate=addend["gate"], scale=addend["scale"], norm_weight=nw,
+                                           norm_eps=ne, out_dtype=ctx.dtype if nw is not None else None)
+            return x, nxt
+        rounded = norm32_ops.stream_update(full, addend["y"], gate=addend["gate"], scale=addend["scale"],
+                                           out_dtype=ctx.dtype)
+        y = self.token_input.forward(ctx, rounded)
+        nxt = norm32_ops.stream_update(full, y, rms_weight=self.token_input.norm_weight, rms_eps=self.token_input.eps,
+                                       norm_weight=nw, norm_eps=ne, out_dtype=ctx.dtype if nw is not None else None)
+        return x, nxt

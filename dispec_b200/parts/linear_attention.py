@@ -11,7 +11,11 @@ by its root mean square (no gain), the heads are multiplied by silu(W_g h) and p
 sigmoid(W_f h + bias), a_t = f_t, b_t = 1 - f_t, q_t = silu(W_q h); every head's o is RMS-normed
 with one gain of size vdim shared by the heads, then projected.
 
-Both run one fused projection, the recurrence kernel (which forms a_t, b_t, q_t from the raw
+``lightning``: a fixed decay per head, q, k and v all pass through silu, a_t = decay_h, b_t = k_t,
+no other scale; the concatenated heads are RMS-normed together with one gain over all of them,
+multiplied by sigmoid(W_g h) and projected.
+
+All run one fused projection, the recurrence kernel (which forms a_t, b_t, q_t from the raw
 projection rows in 32-bit), the per-head norm kernel and the output projection.
 """
 from __future__ import annotations
@@ -99,3 +103,37 @@ class HGRN2(_MatrixStateMixer):
             ctx.positions, gate_bias=self.f_bias, lower=self.lower)
         normed = norm32_ops.head_norm_gate(o, H, self.eps, x.dtype, gain=self.gain)
         return ops.linear(normed, self.w_o, out_dtype=torch.float32)
+
+
+@register_part("mixer", "lightning")
+class Lightning(_MatrixStateMixer):
+    def __init__(self, hidden_size: int, num_heads: int, dim: int, vdim: int, decay, eps: float):
+        super().__init__(hidden_size, num_heads, dim, vdim, eps)
+        decay = [float(v) for v in decay]
+        if len(decay) != num_heads:
+            raise ValueError(f"lightning: {len(decay)} decays for {num_heads} heads")
+        self.decay_values = decay
+        self.decay = self.gain = None
+
+    def tensor_specs(self):
+        h, H, d, dv = self.hidden_size, self.num_heads, self.dim, self.vdim
+        return {"q.weight": TensorSpec((H * d, h)), "k.weight": TensorSpec((H * d, h)),
+                "v.weight": TensorSpec((H * dv, h)), "g.weight": TensorSpec((H * dv, h)),
+                "norm.weight": TensorSpec((H * dv,), dtype="float32", init="one_plus_normal"),
+                "o.weight": TensorSpec((h, H * dv))}
+
+    def load(self, tensors):
+        self.w_in = torch.cat([tensors["q.weight"], tensors["k.weight"], tensors["v.weight"],
+                               tensors["g.weight"]], dim=0).contiguous()
+        self.w_o, self.gain = tensors["o.weight"], tensors["norm.weight"]
+        self.decay = torch.tensor(self.decay_values, dtype=torch.float32, device=self.w_o.device)
+
+    def forward(self, ctx, x, cache, state):
+        H, d, dv = self.num_heads, self.dim, self.vdim
+        proj = ops.linear(x, self.w_in, out_dtype=torch.float32)  # [T, q | k | v | g]
+        o = rec_ops.linear_recurrence(
+            proj, 0, H * d, 2 * H * d, rec_ops.FIXED_DECAY, H, d, dv, state.buffer, state.slots, ctx.q_start,
+            ctx.positions, decay=self.decay, silu_inputs=True)
+        gated = norm32_ops.head_norm_gate(o, 1, self.eps, x.dtype, gain=self.gain,
+                                          gate=proj[:, 2 * H * d + H * dv:], gate_kind="sigmoid")
+        return ops.linear(gated, self.w_o, out_dtype=torch.float32)

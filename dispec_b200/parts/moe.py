@@ -1,0 +1,51 @@
+"""Mixture-of-experts feed-forward with grouped routing.
+
+Scores s = softmax(W_router h) over all experts, in 32-bit (the router matrix stays float32 in
+every mode).  The experts form ``num_groups`` equal runs of neighbours; a group's score is its
+largest score, and only experts of the ``keep_groups`` best groups can be chosen; of those the
+``top`` largest scores are the token's experts, with their scores as weights (not renormalised).
+Expert e: W_down_e act(W_up_e h), act the square of relu, no biases.  The output is the weighted
+sum.  Everything runs on the device (``ops.moe``): no count ever visits the host."""
+from __future__ import annotations
+
+import torch
+
+from dispec_b200.ops import moe as moe_ops
+from dispec_b200.parts.base import FeedForward, TensorSpec
+from dispec_b200.registry import register_part
+
+
+@register_part("feed_forward", "grouped_moe")
+class GroupedMoE(FeedForward):
+    def __init__(self, hidden_size: int, intermediate_size: int, num_experts: int, top: int,
+                 num_groups: int = 1, keep_groups: int = 1):
+        if num_experts <= 0 or num_groups <= 0 or num_experts % num_groups:
+            raise ValueError(f"grouped_moe: {num_experts} experts do not form {num_groups} equal groups")
+        if not 0 < keep_groups <= num_groups:
+            raise ValueError(f"grouped_moe: keep_groups={keep_groups} outside 1..{num_groups}")
+        if not 0 < top <= keep_groups * (num_experts // num_groups):
+            raise ValueError(f"grouped_moe: top={top} experts cannot come from {keep_groups} groups of "
+                             f"{num_experts // num_groups}")
+        self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+        self.num_experts, self.top, self.num_groups, self.keep_groups = num_experts, top, num_groups, keep_groups
+
+    def tensor_specs(self):
+        h, i = self.hidden_size, self.intermediate_size
+        specs = {"router.weight": TensorSpec((self.num_experts, h), dtype="float32")}
+        for e in range(self.num_experts):
+            specs[f"experts.{e}.up.weight"] = TensorSpec((i, h))
+            specs[f"experts.{e}.down.weight"] = TensorSpec((h, i))
+        return specs
+
+    def load(self, tensors):
+        E = self.num_experts
+        self.w_router = tensors["router.weight"]
+        self.w_up = torch.stack([tensors[f"experts.{e}.up.weight"] for e in range(E)]).contiguous()
+        self.w_down = torch.stack([tensors[f"experts.{e}.down.weight"] for e in range(E)]).contiguous()
+
+    def forward(self, ctx, x):
+        ids, wts = moe_ops.route(x, self.w_router, self.num_groups, self.keep_groups, self.top)
+        plan = moe_ops.plan(ids, self.num_experts)
+        a = moe_ops.expert_product(plan, x, self.w_up, x.dtype, rows_are_tokens=True, scatter=False, square_relu=True)
+        y = moe_ops.expert_product(plan, a, self.w_down, torch.float32, rows_are_tokens=False, scatter=True)
+        return moe_ops.combine(y, wts, ids)

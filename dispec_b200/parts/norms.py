@@ -79,3 +79,25 @@ class RMSNorm32(Norm):
         full, rounded = norm32_ops.sum_norm(src, self.weight, self.eps, delta=delta, alpha=alpha,
                                             out32=into, out_dtype=ctx.dtype)
         return WideStream(full, rounded)
+
+
+@register_part("norm", "layer_norm_f32")
+class LayerNorm32(Norm):
+    """y = (x - mean) / sqrt(var + eps) * w with a gain and no bias (var: the mean of the squared
+    deviations), everything in 32-bit; the gain is float32 in every mode.  Reads a 32-bit stream
+    (``WideStream``) or a plain tensor; the result comes in ``ctx.dtype`` (what a product reads)."""
+
+    def __init__(self, hidden_size: int, eps: float):
+        self.hidden_size = hidden_size
+        self.eps = float(eps)
+        self.weight = None
+
+    def tensor_specs(self):
+        return {"weight": TensorSpec((self.hidden_size,), dtype="float32", init="one_plus_normal")}
+
+    def load(self, tensors):
+        self.weight = tensors["weight"]
+
+    def forward(self, ctx, x, rows=None):
+        full = x.full if isinstance(x, WideStream) else x
+        return norm32_ops.layer_norm(full, self.weight, self.eps, ctx.dtype, rows=rows)

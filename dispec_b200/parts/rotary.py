@@ -16,10 +16,14 @@ from dispec_b200.registry import register_part
 
 @register_part("position_encoding", "rotary")
 class RotaryEncoding(PositionEncoding):
-    def __init__(self, head_dim: int, theta: float, rotary_dim: int | None = None, layout: str = "halves"):
+    def __init__(self, head_dim: int, theta: float, rotary_dim: int | None = None, layout: str = "halves",
+                 exact_table: bool = False):
         if layout not in ("halves", "interleaved"):
             raise ValueError(f"rotary layout {layout!r} is not one of 'halves', 'interleaved'")
         self.layout = layout
+        # True: the frequencies are formed in 64-bit and rounded once to float32 (the nearest float32
+        # to theta^(-2i/rotary_dim)); False: in float32 throughout, as the reference's table is
+        self.exact_table = bool(exact_table)
         self.head_dim = head_dim
         self.theta = float(theta)
         self.rotary_dim = head_dim if rotary_dim is None else rotary_dim
@@ -28,7 +32,8 @@ class RotaryEncoding(PositionEncoding):
         self.inv_freq = None
 
     def prepare(self, device):
-        exponent = torch.arange(0, self.rotary_dim, 2, dtype=torch.float32) / self.rotary_dim
+        wide = torch.float64 if self.exact_table else torch.float32
+        exponent = torch.arange(0, self.rotary_dim, 2, dtype=wide) / self.rotary_dim
         self.inv_freq = (1.0 / (self.theta ** exponent)).to(torch.float32).to(device)
 
     def rotation(self):
