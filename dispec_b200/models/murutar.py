@@ -76,9 +76,9 @@ class MurutarConfig(ModelConfig):
                 if _window(m) < 0:
                     raise ConfigError(f"{at}: mask.size must not be negative")
                 if m.get("v_mix"):
-                    width = m["kv_heads"] * m["vdim"]
+                    width = (m["kv_heads"], m["vdim"])
                     if mixed_width is not None and width != mixed_width:
-                        raise ConfigError(f"{at}: v_mix layers must agree in kv_heads * vdim ({width} vs {mixed_width})")
+                        raise ConfigError(f"{at}: v_mix layers must agree in (kv_heads, vdim): {width} vs {mixed_width}")
                     mixed_width = width
             elif len(m["decay"]) != m["heads"]:
                 raise ConfigError(f"{at}: {len(m['decay'])} decays for {m['heads']} heads")

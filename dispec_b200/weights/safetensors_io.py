@@ -106,7 +106,7 @@ def write_safetensors(path: str, tensors: dict, metadata: dict | None = None) ->
         f.write(blob)
         for t in ordered:
             if t.numel():
-                f.write(memoryview(t.view(torch.uint8).reshape(-1).numpy()))
+                f.write(memoryview(t.reshape(-1).view(torch.uint8).numpy()))
 
 
 class CheckpointFolder:

@@ -114,6 +114,10 @@ def dense_ff(h, w, p, mlp):
     return (g * torch.sigmoid(1.702 * g) * (u + 1.0)) @ w[p + "down"].T
 
 
+ROUTING_MARGINS = None  # a list: route() appends (token, how far the choice was from going the other way)
+_TOKEN = 0  # the token moe_ff is at
+
+
 def route(scores, router):
     """scores [experts] -> indices of the chosen experts: the ``top`` largest scores among the
     experts of the ``keep`` groups (equal runs of neighbours) whose largest score is largest."""
@@ -125,13 +129,24 @@ def route(scores, router):
     for g in kept.tolist():
         allowed[g * per:(g + 1) * per] = True
     masked = torch.where(allowed, scores, torch.full_like(scores, -1.0))
-    return torch.topk(masked, top).indices
+    chosen = torch.topk(masked, top).indices
+    if ROUTING_MARGINS is not None:
+        # log-ratio (= difference of router logits) between the last one in and the first one out
+        if keep < n_groups:
+            order = torch.sort(best, descending=True).values
+            ROUTING_MARGINS.append((_TOKEN, float(torch.log(order[keep - 1] / order[keep]))))
+        order = torch.sort(masked, descending=True).values
+        if top < int(allowed.sum()):
+            ROUTING_MARGINS.append((_TOKEN, float(torch.log(order[top - 1] / order[top]))))
+    return chosen
 
 
 def moe_ff(h, w, p, mlp):
     router = mlp["router"]
     out = torch.zeros(h.shape[0], w[p + "e0.down"].shape[0], dtype=F)
+    global _TOKEN
     for t in range(h.shape[0]):
+        _TOKEN = t
         s = torch.softmax(w[p + "router"] @ h[t], dim=0)
         for e in route(s, router).tolist():
             a = torch.relu(w[f"{p}e{e}.up"] @ h[t]) ** 2
