@@ -609,6 +609,139 @@ def puludra_points(args, pk: dict) -> dict:
     return out
 
 
+# ------------------------------------------------------------ Murutar beside Puludra at equal size
+# Murutar's closest relative in this package is Puludra (recurrent and attention mixers in turn on
+# a 32-bit residual stream); both at the same width, depth, vocabulary, heads and feed-forward width.
+# Murutar's layers: lightning + dense, attention + dense, lightning + experts, attention + experts,
+# twice; a window of 1,024 keys; 16 experts of which 2 are used, of half the dense width each, so
+# that a token passes as many feed-forward weights as in a dense layer.
+MURUTAR_SHAPES = {
+    "1.5b": dict(width=1536, heads=12, kv_heads=2, dim=128, vdim=128, rot=64, window=1024, ff=8960, vocab=151936,
+                 experts=16, top=2, groups=4, keep=2, side=64),
+    "7b": dict(width=3584, heads=28, kv_heads=4, dim=128, vdim=128, rot=64, window=1024, ff=18944, vocab=152064,
+               experts=16, top=2, groups=4, keep=2, side=64),
+}
+MURUTAR_LAYERS = 8
+
+
+def murutar_config(shape: str) -> dict:
+    z = MURUTAR_SHAPES[shape]
+    H = z["heads"]
+    dense = {"kind": "dense", "ff": z["ff"], "limit": 7.0}
+    moe = {"kind": "moe", "expert": {"ff": z["ff"] // z["top"]},
+           "router": {"experts": z["experts"], "top": z["top"], "groups": {"count": z["groups"], "keep": z["keep"]}}}
+    att = lambda mlp: {"type": "attention", "mlp": mlp,
+                       "mixer": {"heads": H, "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"],
+                                 "mask": {"size": z["window"]}, "rot": {"base": 1e6, "dims": z["rot"]},
+                                 "scale": z["dim"] ** -0.5, "v_mix": True}}
+    lig = lambda mlp: {"type": "lightning", "mlp": mlp,
+                       "mixer": {"heads": H, "dim": z["dim"], "vdim": z["vdim"],
+                                 "decay": [1 - 2.0 ** (-5 - 3 * i / max(H - 1, 1)) for i in range(H)]}}
+    return {"architecture": "Murutar", "vocab": z["vocab"], "width": z["width"], "embedding": {"scale": z["width"] ** 0.5},
+            "norm": {"eps": 1e-6}, "logit_softcap": 30.0, "token_side": {"dim": z["side"]},
+            "layers": [lig(dense), att(dense), lig(moe), att(moe)] * (MURUTAR_LAYERS // 4)}
+
+
+def murutar_bytes_and_flops(cfg: dict):
+    """(weight bytes a decode step of batch b reads, cache bytes per token and live request as a
+    function of the context, state bytes per request, FLOPs of a prompt of T tokens)."""
+    W, V = cfg["width"], cfg["vocab"]
+    side = (cfg.get("token_side") or {}).get("dim", 0)
+    fixed, cache_layers, state_bytes, attn, rec = 0, [], 0, [], 0
+    expert_layers = []  # (experts, top, weights of one expert)
+    for e in cfg["layers"]:
+        m = e["mixer"]
+        n = W * W  # the gate of the mixer's result
+        if e["type"] == "attention":
+            H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            n += (H * d + G * d + G * dv) * W + W * H * dv
+            cache_layers.append((G * (d + dv) * 2, m["mask"]["size"]))
+            attn.append((H * (d + dv), m["mask"]["size"]))
+        else:
+            H, d, dv = m["heads"], m["dim"], m["vdim"]
+            n += (2 * H * d + 2 * H * dv) * W + W * H * dv
+            state_bytes += 2 * H * d * dv * 4
+            rec += 4 * H * d * dv
+        mlp = e.get("mlp")
+        if mlp is not None:
+            n += W * W
+            if mlp["kind"] == "dense":
+                n += 3 * mlp["ff"] * W
+            else:
+                r = mlp["router"]
+                n += r["experts"] * W * 2  # float32 router
+                expert_layers.append((r["experts"], r["top"], 2 * mlp["expert"]["ff"] * W))
+        n += 2 * side * W
+        fixed += n
+
+    def weight_bytes(batch):
+        return 2 * (fixed + V * W + sum(min(E, batch * top) * w for E, top, w in expert_layers))
+
+    def cache_bytes(ctx):
+        return sum(per * (min(ctx, win) if win else ctx) for per, win in cache_layers)
+
+    def prefill_flops(T):
+        f = 2 * T * (fixed + sum(top * w for _, top, w in expert_layers)) + rec * T + 2 * V * W
+        for per, win in attn:  # scores and weighted sums: 2 flops per (query, key, channel)
+            keys = sum(min(t + 1, win) if win else t + 1 for t in range(T))
+            f += 2 * per * keys
+        return f
+
+    total = 2 * (fixed + V * W + sum(E * w for E, _, w in expert_layers))
+    return weight_bytes, cache_bytes, state_bytes, prefill_flops, total
+
+
+def murutar_points(args, pk: dict) -> dict:
+    """Prefill (2,048 tokens in one step) and decode (batch 1, 8, 64 at 1,024 tokens of context,
+    replayed from captured graphs) of Murutar and of Puludra at equal width, depth, vocabulary,
+    heads and feed-forward width, each with the fraction of its own roofline (bytes a decode step
+    must read over the measured copy bandwidth; prefill FLOPs over the measured bf16 peak)."""
+    import torch
+    from dispec_b200 import load_model_config
+    from dispec_b200.engine import ModelRunner
+    from dispec_b200.weights import load_random_model
+    out = {"only": "murutar", "layers": MURUTAR_LAYERS, "prompt_len": PROMPT_LEN, "prefill_tokens": PREFILL_TOKENS,
+           "peaks": pk}
+    steps, warmup = max(20, min(args.steps, 50)), max(3, args.warmup // 2)
+    per_req = (PROMPT_LEN + NEW_TOKENS + steps + warmup + PAGE_SIZE) // PAGE_SIZE + 1
+    shapes = ["1.5b"] if args.no_other_shapes else list(MURUTAR_SHAPES)
+    for shape in shapes:
+        for family in ("murutar", "puludra"):
+            if family == "murutar":
+                cfg_dict = murutar_config(shape)
+                weight_bytes, cache_bytes, state_bytes, prefill_flops, total = murutar_bytes_and_flops(cfg_dict)
+            else:
+                cfg_dict = puludra_config(shape)
+                wb, per_token, state_bytes, prefill_flops = puludra_bytes_and_flops(cfg_dict)
+                weight_bytes, cache_bytes, total = (lambda b, wb=wb: wb), (lambda c, p=per_token: c * p), wb
+            vocab = cfg_dict["vocab"]
+            model = load_random_model(load_model_config(cfg_dict), 5, STD, "bfloat16", "cuda:0")
+            torch.cuda.synchronize()
+            key = f"{family}_{shape}"
+            out[f"{key}_weight_gb"] = round(total / 1e9, 3)
+            for b in (1, 8, 64):
+                r = ModelRunner(model, page_size=PAGE_SIZE, num_pages=max(b * per_req, 160), max_num_seqs=max(b, 8),
+                                cuda_graph=True)
+                ms, launches, ctx = decode_direct(r, random_prompts(b, PROMPT_LEN, vocab, 13 + b), steps, warmup)
+                step_bytes = weight_bytes(b) + b * (cache_bytes(ctx) + state_bytes)
+                out[f"{key}_decode_b{b}"] = round(b * 1000.0 / ms, 1)
+                out[f"{key}_decode_b{b}_ms"] = round(ms, 4)
+                out[f"{key}_decode_b{b}_hbm_frac"] = round(step_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+                out[f"{key}_decode_b{b}_launches_per_step"] = launches // steps
+                print(f"bench: {key} decode at batch {b}: {ms:.3f} ms a step", file=sys.stderr, flush=True)
+                if b == 1:
+                    pms = prefill_time(r, random_prompts(1, PREFILL_TOKENS, vocab, 12)[0], repeats=3)
+                    out[f"{key}_prefill"] = round(PREFILL_TOKENS / pms * 1000.0, 1)
+                    out[f"{key}_prefill_ms"] = round(pms, 3)
+                    out[f"{key}_prefill_frac"] = round(prefill_flops(PREFILL_TOKENS) / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)
+                del r
+                torch.cuda.empty_cache()
+            del model
+            torch.cuda.empty_cache()
+            print(f"bench: {key} done", file=sys.stderr, flush=True)
+    return out
+
+
 def run_ours(args) -> dict:
     import torch
     from dispec_b200 import load_model_config
@@ -625,6 +758,8 @@ def run_ours(args) -> dict:
         return decode_timeline(args)
     if args.only == "puludra":
         return puludra_points(args, peaks())
+    if args.only == "murutar":
+        return murutar_points(args, peaks())
     cfg_dict = dict(BENCH_CONFIG)
     seed = SEED
     if args.shape != "1.5b":
@@ -794,13 +929,14 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (recorded)")
     ap.add_argument("--shape", choices=["1.5b", "7b", "14b"], default="1.5b",
                     help="layer sizes: Qwen2.5-1.5B (the default and the recorded configuration), 7B or 14B")
-    ap.add_argument("--only", choices=["decode", "prefill", "timeline", "mma-rate", "tma-rate", "attn-prefill", "puludra"], default=None,
+    ap.add_argument("--only", choices=["decode", "prefill", "timeline", "mma-rate", "tma-rate", "attn-prefill", "puludra", "murutar"], default=None,
                     help="profiling aid: run one phase only and print a short line; timeline: where the time of the "
                          "decode step's products and attention goes (a build with timestamps); mma-rate: cycles per "
                          "tcgen05.mma for one to four issuing threads; tma-rate: bytes a clock an SM takes in from "
                          "the L2 by TMA, by the size of a request; attn-prefill: the attention kernel for portions of prompts "
                          "alone, by shape, length and the order of the pages; puludra: prefill and decode of the Puludra design beside "
-                         "Qwen2 at equal width, depth, vocabulary and feed-forward width (eight layers each), with roofline fractions")
+                         "Qwen2 at equal width, depth, vocabulary and feed-forward width (eight layers each), with roofline fractions; "
+                         "murutar: the same for the Murutar design beside Puludra")
     ap.add_argument("--batch", type=int, default=BATCH, help="batch of the --only decode phase")
     ap.add_argument("--max-key-ranges", type=int, default=0,
                     help="profiling aid: cap on the key ranges per decoded row beyond one cluster (1: none)")

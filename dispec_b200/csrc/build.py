@@ -173,6 +173,12 @@ def prefill_attention_library(head_dim: int) -> str:
     return specialised_library(f"attn_tcgen05_d{head_dim}", "attn_tcgen05.cu", {"DSP_HEAD_DIM": head_dim})
 
 
+def sink_attention_library(key_dim: int, value_dim: int) -> str:
+    """The tensor-core attention with a sink and widths of their own for keys and values."""
+    return specialised_library(f"attn_sink_mma_k{key_dim}_v{value_dim}", "attn_sink_mma.cu",
+                               {"DSP_DK": key_dim, "DSP_DV": value_dim})
+
+
 # Kernels only some mixers need, each a library of its own that is built when a model with such
 # a mixer first runs: name -> source file.
 MIXER_LIBRARIES = {"linear_recurrence": "linear_recurrence.cu", "attn_latent": "attn_latent.cu",

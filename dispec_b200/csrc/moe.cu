@@ -13,12 +13,14 @@
 //                    (B: [experts, N, K]); a_row / c_row are optional index lists (gather, scatter).
 //                    act 0: none, 1: the square of relu.  Every output is one chain of fused
 //                    multiply-adds in ascending k, so a pair's result depends on nothing but its own
-//                    row and its expert.
+//                    row and its expert.  With `tensor_cores` (bfloat16 operands): mma.sync tiles of
+//                    64 pairs; the plan must have been made for tiles of that many rows.
 //   dsp_moe_combine  y[t] = sum_k weight[t, k] * P[t * top + k], in ascending k.
 #include "common.cuh"
 
 namespace {
 constexpr int TILE_ROWS = 32, TILE_COLS = 64, TILE_K = 32;
+constexpr int MMA_ROWS = 64, MMA_COLS = 128, MMA_K = 32, MMA_PAD = 8, MMA_STAGES = 3;
 
 struct Best {
   float v;
@@ -98,7 +100,7 @@ moe_route_kernel(const void* __restrict__ h, int h_dtype, long ldh, const float*
 }
 
 __global__ void __launch_bounds__(1024)
-moe_plan_kernel(const int* __restrict__ ids, int n_pairs, int E, int* __restrict__ offsets,
+moe_plan_kernel(const int* __restrict__ ids, int n_pairs, int E, int tile_rows_max, int* __restrict__ offsets,
                 int* __restrict__ sorted_pair, int* __restrict__ tile_expert, int* __restrict__ tile_row0,
                 int* __restrict__ tile_rows, int* __restrict__ n_tiles, int max_tiles) {
   extern __shared__ int ism[];
@@ -116,10 +118,10 @@ moe_plan_kernel(const int* __restrict__ ids, int n_pairs, int E, int* __restrict
     int o = 0, nt = 0;
     for (int e = 0; e < E; ++e) {
       off[e] = o;
-      for (int r = 0; r < cnt[e] && nt < max_tiles; r += TILE_ROWS, ++nt) {
+      for (int r = 0; r < cnt[e] && nt < max_tiles; r += tile_rows_max, ++nt) {
         tile_expert[nt] = e;
         tile_row0[nt] = o + r;
-        tile_rows[nt] = min(TILE_ROWS, cnt[e] - r);
+        tile_rows[nt] = min(tile_rows_max, cnt[e] - r);
       }
       o += cnt[e];
     }
@@ -197,6 +199,121 @@ moe_product_kernel(const T* __restrict__ A, long lda, const int* __restrict__ a_
   }
 }
 
+
+// The same product on tensor cores (bfloat16 operands, 32-bit accumulators): a tile of up to 64
+// pairs x 128 outputs per block of four warps (2 x 2, each 32 x 64 in m16n8k16 pieces), k in
+// blocks of 32 through a ring of three cp.async stages; A rows are gathered by their indices.
+// K and the row strides are multiples of 8 elements and the operands 16-byte aligned.
+__device__ __forceinline__ void cp16(void* smem, const void* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem));
+}
+__device__ __forceinline__ void ldsm4(uint32_t (&r)[4], const void* smem) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"((uint32_t)__cvta_generic_to_shared(smem)));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(128)
+moe_product_mma_kernel(const bf16* __restrict__ A, long lda, const int* __restrict__ a_rows, int a_div,
+                       const bf16* __restrict__ B, void* __restrict__ C, int c_dtype, long ldc,
+                       const int* __restrict__ c_rows, const int* __restrict__ tile_expert,
+                       const int* __restrict__ tile_row0, const int* __restrict__ tile_rows,
+                       const int* __restrict__ n_tiles, int N, int K, int act) {
+  const int tile = blockIdx.x;
+  if (tile >= *n_tiles) return;
+  __shared__ __align__(16) bf16 As[MMA_STAGES][MMA_ROWS][MMA_K + MMA_PAD];
+  __shared__ __align__(16) bf16 Bs[MMA_STAGES][MMA_COLS][MMA_K + MMA_PAD];
+  __shared__ long arow[MMA_ROWS], crow[MMA_ROWS];
+  const int e = tile_expert[tile], r0 = tile_row0[tile], nr = tile_rows[tile];
+  const int n0 = blockIdx.y * MMA_COLS;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int wm = warp >> 1, wn = warp & 1;  // the warp's 32 rows and 64 columns of the tile
+  if (tid < MMA_ROWS) {
+    const int i = r0 + tid;
+    arow[tid] = tid < nr ? (a_rows ? (long)(a_rows[i] / a_div) : (long)i) : -1;
+    crow[tid] = tid < nr ? (c_rows ? (long)c_rows[i] : (long)i) : -1;
+  }
+  __syncthreads();
+  const bf16* Be = B + (size_t)e * N * K;
+  auto load = [&](int stage, int k0) {
+    for (int c = tid; c < MMA_ROWS * (MMA_K / 8); c += 128) {
+      const int r = c / (MMA_K / 8), k = (c % (MMA_K / 8)) * 8;
+      bf16* dst = &As[stage][r][k];
+      if (arow[r] >= 0 && k0 + k < K)
+        cp16(dst, A + (size_t)arow[r] * lda + k0 + k);
+      else
+        *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+    }
+    for (int c = tid; c < MMA_COLS * (MMA_K / 8); c += 128) {
+      const int n = c / (MMA_K / 8), k = (c % (MMA_K / 8)) * 8;
+      bf16* dst = &Bs[stage][n][k];
+      if (n0 + n < N && k0 + k < K)
+        cp16(dst, Be + (size_t)(n0 + n) * K + k0 + k);
+      else
+        *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+    }
+    asm volatile("cp.async.commit_group;\n");
+  };
+  float acc[2][8][4] = {};
+  const int nk = (K + MMA_K - 1) / MMA_K;
+  for (int s = 0; s < MMA_STAGES - 1; ++s) {
+    if (s < nk)
+      load(s, s * MMA_K);
+    else
+      asm volatile("cp.async.commit_group;\n");
+  }
+  for (int kt = 0; kt < nk; ++kt) {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(MMA_STAGES - 2));
+    __syncthreads();  // stage kt has landed for everyone; stage kt - 1 has been read by everyone
+    if (kt + MMA_STAGES - 1 < nk)
+      load((kt + MMA_STAGES - 1) % MMA_STAGES, (kt + MMA_STAGES - 1) * MMA_K);
+    else
+      asm volatile("cp.async.commit_group;\n");
+    const int st = kt % MMA_STAGES;
+#pragma unroll
+    for (int kk = 0; kk < MMA_K; kk += 16) {
+      uint32_t a[2][4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) ldsm4(a[i], &As[st][wm * 32 + i * 16 + (lane & 15)][kk + (lane >> 4) * 8]);
+#pragma unroll
+      for (int j = 0; j < 8; j += 2) {
+        uint32_t b[4];  // two blocks of eight columns: (n, k 0-7), (n, k 8-15), (n + 8, k 0-7), (n + 8, k 8-15)
+        ldsm4(b, &Bs[st][wn * 64 + j * 8 + (lane & 7) + ((lane >> 4) << 3)][kk + ((lane >> 3) & 1) * 8]);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          mma16816(acc[i][j], a[i], b[0], b[1]);
+          mma16816(acc[i][j + 1], a[i], b[2], b[3]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const long cr = crow[wm * 32 + i * 16 + half * 8 + (lane >> 2)];
+      if (cr < 0) continue;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          const int n = n0 + wn * 64 + j * 8 + (lane & 3) * 2 + q;
+          if (n >= N) continue;
+          float v = acc[i][j][half * 2 + q];
+          if (act == 1) {
+            v = fmaxf(v, 0.f);
+            v *= v;
+          }
+          st_any(C, c_dtype, (size_t)cr * ldc + n, v);
+        }
+    }
+}
+
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* __restrict__ P, long ldp, const float* __restrict__ wts, const int* __restrict__ ids,
                    float* __restrict__ y, long ldy, long T, int top, int width) {
@@ -212,7 +329,8 @@ moe_combine_kernel(const float* __restrict__ P, long ldp, const float* __restric
 }
 }  // namespace
 
-extern "C" int dsp_moe_tile_rows() { return TILE_ROWS; }
+// Rows of a tile of dsp_moe_product: the tensor-core kernel's (bfloat16) or the 32-bit kernel's.
+extern "C" int dsp_moe_tile_rows(int tensor_cores) { return tensor_cores ? MMA_ROWS : TILE_ROWS; }
 
 extern "C" int dsp_moe_route(const void* h, int h_dtype, long ldh, const float* w, int T, int W, int E, int groups,
                              int keep, int top, int* ids, float* wts, cudaStream_t stream) {
@@ -230,14 +348,16 @@ extern "C" int dsp_moe_route(const void* h, int h_dtype, long ldh, const float* 
   return 0;
 }
 
-extern "C" int dsp_moe_plan(const int* ids, int n_pairs, int E, int* offsets, int* sorted_pair, int* tile_expert,
-                            int* tile_row0, int* tile_rows, int* n_tiles, int max_tiles, cudaStream_t stream) {
+extern "C" int dsp_moe_plan(const int* ids, int n_pairs, int E, int rows_per_tile, int* offsets, int* sorted_pair,
+                            int* tile_expert, int* tile_row0, int* tile_rows, int* n_tiles, int max_tiles,
+                            cudaStream_t stream) {
   DSP_REQUIRE(ids && offsets && sorted_pair && tile_expert && tile_row0 && tile_rows && n_tiles, "dsp_moe_plan: missing operand");
-  DSP_REQUIRE(max_tiles >= n_pairs / TILE_ROWS + E, "dsp_moe_plan: room for %d tiles, %d may be needed", max_tiles,
-              n_pairs / TILE_ROWS + E);
+  DSP_REQUIRE(rows_per_tile == TILE_ROWS || rows_per_tile == MMA_ROWS, "dsp_moe_plan: tiles of %d rows", rows_per_tile);
+  DSP_REQUIRE(max_tiles >= n_pairs / rows_per_tile + E, "dsp_moe_plan: room for %d tiles, %d may be needed", max_tiles,
+              n_pairs / rows_per_tile + E);
   const size_t smem = (size_t)(3 * E + 1) * sizeof(int);
   DSP_REQUIRE(smem <= 48 * 1024, "dsp_moe_plan: %d experts are more than the planning kernel holds", E);
-  DSP_CUDA(launch_plain(moe_plan_kernel, dim3(1), dim3(1024), smem, stream, ids, n_pairs, E, offsets, sorted_pair,
+  DSP_CUDA(launch_plain(moe_plan_kernel, dim3(1), dim3(1024), smem, stream, ids, n_pairs, E, rows_per_tile, offsets, sorted_pair,
                         tile_expert, tile_row0, tile_rows, n_tiles, max_tiles));
   DSP_CHECK_LAUNCH("dsp_moe_plan");
   return 0;
@@ -246,10 +366,21 @@ extern "C" int dsp_moe_plan(const int* ids, int n_pairs, int E, int* offsets, in
 extern "C" int dsp_moe_product(const void* A, int ab_dtype, long lda, const int* a_rows, int a_div, const void* B,
                                void* C, int c_dtype, long ldc, const int* c_rows, const int* tile_expert,
                                const int* tile_row0, const int* tile_rows, const int* n_tiles, int max_tiles, int N,
-                               int K, int act, cudaStream_t stream) {
+                               int K, int act, int tensor_cores, cudaStream_t stream) {
   if (max_tiles == 0 || N == 0) return 0;
   DSP_REQUIRE(A && B && C && tile_expert && tile_row0 && tile_rows && n_tiles && a_div > 0, "dsp_moe_product: missing operand");
   DSP_REQUIRE(act == 0 || act == 1, "dsp_moe_product: unknown activation %d", act);
+  if (tensor_cores) {
+    DSP_REQUIRE(ab_dtype == DSP_BF16 && K % 8 == 0 && lda % 8 == 0 && ((uintptr_t)A % 16) == 0 && ((uintptr_t)B % 16) == 0,
+                "dsp_moe_product: the tensor-core kernel takes 16-byte aligned bfloat16 operands with K and the row "
+                "stride multiples of 8 (K=%d, stride %ld)", K, lda);
+    dim3 mgrid(max_tiles, (N + MMA_COLS - 1) / MMA_COLS);
+    DSP_REQUIRE(mgrid.y <= 65535, "dsp_moe_product: N=%d is too wide", N);
+    DSP_CUDA(launch_plain(moe_product_mma_kernel, mgrid, dim3(128), 0, stream, (const bf16*)A, lda, a_rows, a_div,
+                          (const bf16*)B, C, c_dtype, ldc, c_rows, tile_expert, tile_row0, tile_rows, n_tiles, N, K, act));
+    DSP_CHECK_LAUNCH("dsp_moe_product (tensor cores)");
+    return 0;
+  }
   dim3 grid(max_tiles, (N + TILE_COLS - 1) / TILE_COLS);
   DSP_REQUIRE(grid.y <= 65535, "dsp_moe_product: N=%d is too wide", N);
   if (ab_dtype == DSP_F32) {

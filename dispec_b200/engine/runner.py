@@ -55,12 +55,8 @@ class ModelRunner:
         # otherwise (angles are computed from the position, so no table stands in the way of more)
         limit = max_model_len or model.spec.max_position or (1 << 30)
         self.max_model_len = min(limit, self.cache.capacity_tokens())
-        # page-table width of a captured step: a full group never holds more pages than its pool has;
-        # a window group's table is indexed by logical page (holes behind the window), so its
-        # length follows the context, not the pool
-        longest = max(1, -(-self.max_model_len // page_size))
-        self._graph_pages = [longest if g.window > 0 else max(1, min(c, longest))
-                             for g, c in zip(groups, counts)]
+        self._group_windows = [g.window for g in groups]
+        self._group_pages = list(counts)
         self._graphs: dict = {}
 
     # ---------------------------------------------------------------- request lifecycle
@@ -131,7 +127,20 @@ class ModelRunner:
         for bound in GRAPH_CONTEXT_CLASSES:
             if longest <= bound < self.max_model_len:
                 return bound
-        return self.max_model_len
+        # beyond the listed classes (a model whose groups all have windows has no longest request of
+        # its own): powers of two, so that the page tables of a captured step stay near the context
+        bound = GRAPH_CONTEXT_CLASSES[-1]
+        while bound < longest:
+            bound *= 2
+        return min(bound, self.max_model_len)
+
+    def _graph_pages(self, ctx_bound: int) -> list:
+        """Page-table width per group of a step captured for contexts up to ``ctx_bound``: a full
+        group never holds more pages than its pool has; a window group's table is indexed by
+        logical page (holes behind the window), so its length follows the context, not the pool."""
+        longest = max(1, -(-min(ctx_bound, self.max_model_len) // self.page_size))
+        return [longest if w > 0 else max(1, min(c, longest))
+                for w, c in zip(self._group_windows, self._group_pages)]
 
     def _capture(self, bucket: int, ctx_bound: int) -> dict:
         """Captures one decode step of ``bucket`` single-token rows, none longer than
@@ -140,7 +149,7 @@ class ModelRunner:
         the step's values there first.  Rows beyond the live requests carry position -1 and
         length 0, which the kernels skip."""
         plan = StepPlanLayout([], self.cache, self.model.attention_tile_tokens, self.vocab_size,
-                              pad_seqs=bucket, fixed_pages=self._graph_pages)
+                              pad_seqs=bucket, fixed_pages=self._graph_pages(ctx_bound))
         buffer = torch.empty(plan.total, dtype=torch.int32, device=self.device)
         self.staging.upload(plan.total, plan.fill, into=buffer)
         ctx = plan.context(buffer, self.storage, self.states, self.dtype, self.device)
@@ -172,7 +181,7 @@ class ModelRunner:
         ctx_bound = self._context_class(entries)
         g = self._graphs.get((bucket, ctx_bound)) or self._capture(bucket, ctx_bound)
         plan = StepPlanLayout(entries, self.cache, self.model.attention_tile_tokens, self.vocab_size,
-                              pad_seqs=bucket, fixed_pages=self._graph_pages)
+                              pad_seqs=bucket, fixed_pages=self._graph_pages(ctx_bound))
         assert plan.total == g["total"]
         self.staging.upload(plan.total, plan.fill, into=g["buffer"])
         if plan.num_fed:

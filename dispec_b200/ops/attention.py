@@ -331,16 +331,55 @@ def qkv_rotate_store(qkv: torch.Tensor, positions: torch.Tensor, seq_of_token: t
     return q_out
 
 
+SINK_ROWS_PER_TILE = 64  # query rows (token, head-in-group pairs) of a tile of the tensor-core kernel
+
+
+def sink_mma_supported(group_size: int, key_dim: int, value_dim: int, dtype: torch.dtype = torch.bfloat16) -> bool:
+    """The tensor-core kernel is compiled per pair of widths: multiples of 16, keys up to 256 and
+    values up to 128 wide (the output accumulators live in registers), groups of up to 64 heads."""
+    return (dtype == torch.bfloat16 and key_dim % 16 == 0 and value_dim % 16 == 0 and 16 <= key_dim <= 256
+            and 16 <= value_dim <= 128 and group_size <= SINK_ROWS_PER_TILE)
+
+
 def sink_tokens_per_tile(group_size: int, key_dim: int, value_dim: int):
     """Query tokens per tile that the tensor-core kernel of ``sink_paged_attention`` wants listed
     in the batch (None: the 32-bit kernel runs, which needs no tile list)."""
-    return None
+    if not sink_mma_supported(group_size, key_dim, value_dim):
+        return None
+    return SINK_ROWS_PER_TILE // group_size
+
+
+def sink_attention_tiles(q, k_pool, v_pool, page_table, q_start, ctx_len, tile_seq, tile_tok0, num_tiles, out,
+                         num_heads, num_kv_heads, window, scale, sink) -> torch.Tensor:
+    """The tensor-core kernel over a tile list (``tokens per tile`` = 64 // group)."""
+    num_pages, G, page_size, dk = k_pool.shape
+    dv = v_pool.shape[3]
+    assert q.dtype == k_pool.dtype == v_pool.dtype == out.dtype == torch.bfloat16
+    assert k_pool.is_contiguous() and v_pool.is_contiguous() and q.stride(1) == 1 and out.stride(1) == 1
+    fn = getattr(L.sink_attention_library(dk, dv), f"dsp_attn_sink_mma_k{dk}_v{dv}")
+    rc = fn(L.ptr(q), L.i64(q.stride(0)), L.ptr(k_pool), L.ptr(v_pool), L.ptr(page_table), page_table.stride(0),
+            L.ptr(q_start), L.ptr(ctx_len), L.ptr(tile_seq), L.ptr(tile_tok0), num_tiles, L.ptr(out),
+            L.i64(out.stride(0)), num_heads, num_kv_heads, SINK_ROWS_PER_TILE // (num_heads // num_kv_heads),
+            page_size, num_pages, window, L.f32(scale), int(sink), ctypes.c_void_p(_device_error_address(q.device)),
+            L.stream_handle())
+    L.LaunchCounter.n += 1
+    if rc != 0:
+        raise L.KernelError(f"dsp_attn_sink_mma_k{dk}_v{dv}: {_MMA_ERRORS.get(rc, rc)}")
+    return out
 
 
 def sink_paged_attention(ctx, q: torch.Tensor, cache, out: torch.Tensor, num_heads: int, num_kv_heads: int,
                          key_dim: int, value_dim: int, window: int, scale: float, sink: bool) -> torch.Tensor:
     """Attention of the step over pools whose keys and values have widths of their own, with an
-    optional sink in the softmax: q [T, H * Dk] (already turned), out [T, H * Dv]."""
+    optional sink in the softmax: q [T, H * Dk] (already turned), out [T, H * Dv].  bfloat16 runs
+    on the tensor-core kernel where it is built for the sizes and the batch lists its tiles;
+    everything else (and float32 always) on the 32-bit kernel."""
+    group = num_heads // num_kv_heads
+    tpt = sink_tokens_per_tile(group, key_dim, value_dim)
+    if q.dtype == torch.bfloat16 and tpt is not None and tpt in ctx.attention_tiles:
+        tile_seq, tile_tok0, num_tiles = ctx.attention_tiles[tpt]
+        return sink_attention_tiles(q, cache.key_pool, cache.value_pool, cache.page_table, ctx.q_start, ctx.ctx_len,
+                                    tile_seq, tile_tok0, num_tiles, out, num_heads, num_kv_heads, window, scale, sink)
     return paged_attention_generic(q, q.stride(0), cache.key_pool, cache.value_pool, cache.page_table,
                                    ctx.positions, ctx.seq_of_token, out, num_heads, num_kv_heads, key_dim,
                                    window, scale, sink=sink)

@@ -61,6 +61,16 @@ def prefill_attention_library(head_dim: int) -> ctypes.CDLL:
     return _special[key]
 
 
+def sink_attention_library(key_dim: int, value_dim: int) -> ctypes.CDLL:
+    key = f"attn_sink_mma_k{key_dim}_v{value_dim}"
+    if key not in _special:
+        core()
+        with _lock:
+            if key not in _special:
+                _special[key] = ctypes.CDLL(build.sink_attention_library(key_dim, value_dim))
+    return _special[key]
+
+
 def mixer_library(name: str) -> ctypes.CDLL:
     """A library of kernels that only some mixers need (``build.MIXER_LIBRARIES``)."""
     if name not in _special:

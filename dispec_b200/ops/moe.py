@@ -41,21 +41,28 @@ class ExpertPlan:
     max_tiles: int
     num_pairs: int
     top: int
+    tensor_cores: bool  # tiles of as many rows as the tensor-core kernel takes
 
 
-def plan(ids: torch.Tensor, num_experts: int) -> ExpertPlan:
+def tensor_cores_supported(dtype: torch.dtype, *inner_sizes: int) -> bool:
+    """The tensor-core product takes bfloat16 operands whose inner sizes are multiples of 8."""
+    return dtype == torch.bfloat16 and all(k % 8 == 0 for k in inner_sizes)
+
+
+def plan(ids: torch.Tensor, num_experts: int, tensor_cores: bool = False) -> ExpertPlan:
     T, top = ids.shape
     n = T * top
     lib = _lib()
-    max_tiles = n // int(lib.dsp_moe_tile_rows()) + num_experts
+    rows = int(lib.dsp_moe_tile_rows(int(tensor_cores)))
+    max_tiles = n // rows + num_experts
     dev = ids.device
     sorted_pair = torch.empty(max(n, 1), dtype=torch.int32, device=dev)
     offsets = torch.empty(num_experts + 1, dtype=torch.int32, device=dev)
     tiles = torch.empty((3, max_tiles), dtype=torch.int32, device=dev)
     n_tiles = torch.empty(1, dtype=torch.int32, device=dev)
-    L.check(lib.dsp_moe_plan(L.ptr(ids), n, num_experts, L.ptr(offsets), L.ptr(sorted_pair), L.ptr(tiles[0]),
+    L.check(lib.dsp_moe_plan(L.ptr(ids), n, num_experts, rows, L.ptr(offsets), L.ptr(sorted_pair), L.ptr(tiles[0]),
                              L.ptr(tiles[1]), L.ptr(tiles[2]), L.ptr(n_tiles), max_tiles, L.stream_handle()))
-    return ExpertPlan(sorted_pair, offsets, tiles, n_tiles, max_tiles, n, top)
+    return ExpertPlan(sorted_pair, offsets, tiles, n_tiles, max_tiles, n, top, tensor_cores)
 
 
 def expert_product(p: ExpertPlan, a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, *,
@@ -72,7 +79,7 @@ def expert_product(p: ExpertPlan, a: torch.Tensor, w: torch.Tensor, out_dtype: t
         L.ptr(a), L.dtype_code(a.dtype), L.i64(a.stride(0)), L.ptr(p.sorted_pair if rows_are_tokens else None),
         p.top if rows_are_tokens else 1, L.ptr(w), L.ptr(out), L.dtype_code(out_dtype), L.i64(out.stride(0)),
         L.ptr(p.sorted_pair if scatter else None), L.ptr(p.tiles[0]), L.ptr(p.tiles[1]), L.ptr(p.tiles[2]),
-        L.ptr(p.n_tiles), p.max_tiles, N, K, int(square_relu), L.stream_handle()))
+        L.ptr(p.n_tiles), p.max_tiles, N, K, int(square_relu), int(p.tensor_cores), L.stream_handle()))
     return out[:p.num_pairs]
 
 

@@ -45,7 +45,8 @@ class GroupedMoE(FeedForward):
 
     def forward(self, ctx, x):
         ids, wts = moe_ops.route(x, self.w_router, self.num_groups, self.keep_groups, self.top)
-        plan = moe_ops.plan(ids, self.num_experts)
+        plan = moe_ops.plan(ids, self.num_experts, moe_ops.tensor_cores_supported(x.dtype, self.hidden_size,
+                                                                                   self.intermediate_size))
         a = moe_ops.expert_product(plan, x, self.w_up, x.dtype, rows_are_tokens=True, scatter=False, square_relu=True)
         y = moe_ops.expert_product(plan, a, self.w_down, torch.float32, rows_are_tokens=False, scatter=True)
         return moe_ops.combine(y, wts, ids)

@@ -444,3 +444,78 @@ def test_sink_attention_sees_exactly_the_window(H, G, dk, dv, page, window, pool
     out = out.float().cpu().double().view(T, H, dv)
     assert torch.isfinite(out).all()
     _check_aimed(c, out, H, G, window, scale, 2e-4 if pool_dtype == torch.float32 else 0.02)
+
+
+@pytest.mark.parametrize("H,G,dk,dv,page,window", [(4, 2, 16, 16, 16, 20), (18, 2, 64, 128, 32, 64), (8, 1, 128, 64, 16, 100),
+                                                   (12, 2, 128, 128, 16, 0), (6, 2, 32, 16, 8, 7), (5, 5, 48, 32, 16, 33)])
+@pytest.mark.parametrize("sink", [True, False])
+def test_sink_attention_on_tensor_cores_matches_the_plain_softmax(H, G, dk, dv, page, window, sink):
+    """A step of two single tokens and a portion of a prompt whose tiles end in the middle of a key
+    tile; every query is aimed at one key: the first of the request, both sides of a page border,
+    the first key of its window and the one before it, its own position, the next one (stored,
+    invisible), or nothing (the sink takes the weight).  Scattered pages, NaN everywhere else."""
+    from dispec_b200.ops import attention as A
+    g = torch.Generator().manual_seed(H + dk)
+    lens, q_lens = [3 * page + 5, 200, 9 * page + 7], [1, 1, 45]
+    n_pages = sum(-(-n // page) for n in lens) + 3
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    width = max(-(-n // page) for n in lens)
+    k_pool = torch.full((n_pages, G, page, dk), float("nan"))
+    v_pool = torch.full((n_pages, G, page, dv), float("nan"))
+    tables, keys, vals, qs, stars = [], [], [], [], []
+    aims = ["first", "border-", "border+", "edge_in", "edge_out", "self", "next", None]
+    for s, (n, ql) in enumerate(zip(lens, q_lens)):
+        need = -(-n // page)
+        tables.append([perm.pop() for _ in range(need)] + [-1] * (width - need))
+        kk = torch.randn(n, G, dk, generator=g).bfloat16().float()
+        vv = torch.randn(n, G, dv, generator=g).bfloat16().float()
+        qq = torch.randn(ql, H, dk, generator=g) * 0.05
+        star = []
+        for i in range(ql):
+            p = n - ql + i
+            lo = max(0, p - window + 1) if window else 0
+            a = aims[(i + s) % len(aims)]
+            j = {"first": 0, "border-": page - 1, "border+": page, "edge_in": lo, "edge_out": max(lo - 1, 0), "self": p,
+                 "next": min(p + 1, n - 1), None: None}[a]
+            star.append(j)
+        for j in {j for j in star if j is not None}:
+            kk[j] = (kk[j] * 3.0).bfloat16().float()
+        for i, j in enumerate(star):
+            for h in range(H):
+                if j is None:
+                    qq[i, h] -= 0.5 * kk[:, h // (H // G)].mean(0)
+                else:
+                    kj = kk[j, h // (H // G)]
+                    qq[i, h] += 40.0 * kj / kj.norm() ** 2
+        for j in range(n):
+            k_pool[tables[-1][j // page], :, j % page] = kk[j]
+            v_pool[tables[-1][j // page], :, j % page] = vv[j]
+        keys.append(kk); vals.append(vv); qs.append(qq.bfloat16().float()); stars.append(star)
+    group = H // G
+    assert A.sink_mma_supported(group, dk, dv)
+    tpt = A.sink_tokens_per_tile(group, dk, dv)
+    tiles = [(s, a) for s, ql in enumerate(q_lens) for a in range(0, ql, tpt)]
+    T = sum(q_lens)
+    out = torch.full((T, H * dv), float("nan"), dtype=torch.bfloat16, device="cuda:0")
+    scale = 0.4
+    A.sink_attention_tiles(dev(torch.cat(qs).reshape(T, -1), torch.bfloat16), dev(k_pool, torch.bfloat16),
+                           dev(v_pool, torch.bfloat16), i32(tables), i32([0, 1, 2, 2 + q_lens[2]]), i32(lens),
+                           i32([s for s, _ in tiles]), i32([a for _, a in tiles]), len(tiles), out, H, G, window, scale, sink)
+    out = out.float().cpu().double().view(T, H, dv)
+    assert torch.isfinite(out).all()
+    at = 0
+    for s, (n, ql) in enumerate(zip(lens, q_lens)):
+        q_full = torch.cat([torch.zeros(n - ql, H, dk), qs[s]]).double()
+        if sink:
+            want = plain.sink_window_attention(q_full, keys[s].double(), vals[s].double(), scale, window)[n - ql:]
+        else:
+            want = torch.zeros(ql, H, dv, dtype=torch.float64)
+            for i in range(ql):
+                p = n - ql + i
+                lo = max(0, p - window + 1) if window else 0
+                for h in range(H):
+                    w = torch.softmax((keys[s][lo:p + 1, h // group].double() @ q_full[p, h]) * scale, dim=0)
+                    want[i, h] = w @ vals[s][lo:p + 1, h // group].double()
+        err = (out[at:at + ql] - want).abs().amax(dim=(1, 2))
+        assert err.max() < 0.03 * max(1.0, want.abs().max().item()), (s, int(err.argmax()), stars[s][int(err.argmax())])
+        at += ql
