@@ -11,6 +11,11 @@
 // p - window < j <= p (window 0: every j <= p); positions follow from the request's stored length
 // (ctx_len) and the number of tokens it brings.  A request of length 0 (a padding row of a
 // captured step) is skipped.
+//
+// Key splits (single tokens, whose one tile would otherwise walk its window alone): with
+// splits > 1 the grid's z index takes a share of the tile's key tiles and leaves an unnormalised
+// output with its (max, sum) in the scratch that attn_combine.cu merges; only split 0 starts from
+// the sink's (0, 1), so the sink is counted once.
 #include "common.cuh"
 
 #ifndef DSP_DK
@@ -19,7 +24,7 @@
 
 namespace {
 constexpr int DK = DSP_DK, DV = DSP_DV;
-constexpr int BM = 64, BN = 64, PAD = 8;
+constexpr int BM = 64, BN = 64, PAD = 8;  // BN key rows a tile: two of the block's 128 threads a row
 constexpr int LDK = DK + PAD, LDV = DV + PAD;
 static_assert(DK % 16 == 0 && DV % 16 == 0, "widths are multiples of 16");
 
@@ -52,12 +57,13 @@ attn_sink_mma_kernel(const bf16* __restrict__ q, long ldq, const bf16* __restric
                      const int* __restrict__ q_start, const int* __restrict__ ctx_len,
                      const int* __restrict__ tile_seq, const int* __restrict__ tile_tok0, bf16* __restrict__ out,
                      long ldo, int H, int G, int tpt, int page_size, int num_pages, int window, float scale_log2,
-                     int sink, int* err) {
+                     int sink, int tile_offset, int splits, float* __restrict__ part_o, float* __restrict__ part_ml,
+                     int* err) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* Qs = reinterpret_cast<bf16*>(smem_raw);  // [BM][LDK]
   bf16* Ks = Qs + BM * LDK;                      // [2][BN][LDK]
   bf16* Vs = Ks + 2 * BN * LDK;                  // [2][BN][LDV]
-  const int tile = blockIdx.x, g = blockIdx.y;
+  const int tile = blockIdx.x + tile_offset, g = blockIdx.y, split = blockIdx.z;
   const int seq = tile_seq[tile], tok0 = tile_tok0[tile];
   const int qs = q_start[seq], qlen = q_start[seq + 1] - qs, clen = ctx_len[seq];
   if (clen <= 0 || tok0 >= qlen) return;
@@ -65,7 +71,9 @@ attn_sink_mma_kernel(const bf16* __restrict__ q, long ldq, const bf16* __restric
   const int nt = min(tpt, qlen - tok0), rows = nt * group;
   const int pos0 = clen - qlen + tok0, p1 = pos0 + nt - 1;
   const int lo = window > 0 ? max(0, pos0 - window + 1) : 0;
-  const int nkt = (p1 - lo) / BN + 1;
+  const int nkt_all = (p1 - lo) / BN + 1;
+  const int kt0 = (int)((long)nkt_all * split / splits), kt1 = (int)((long)nkt_all * (split + 1) / splits);
+  const int nkt = kt1 - kt0;  // this block's key tiles: kt0 .. kt1 - 1 (none: it leaves an empty partial)
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int* table = page_table + (size_t)seq * pt_stride;
 
@@ -80,40 +88,49 @@ attn_sink_mma_kernel(const bf16* __restrict__ q, long ldq, const bf16* __restric
   // returns whether one of this thread's key rows had a page id outside the pool
   auto load = [&](int stage, int kt) {
     int bad = 0;
-    const int j0 = lo + kt * BN;
+    const int j0 = lo + (kt0 + kt) * BN;
     bf16* ks = Ks + stage * BN * LDK;
     bf16* vs = Vs + stage * BN * LDV;
-    for (int c = tid; c < BN * (DK / 8 + DV / 8); c += 128) {
-      const int r = c / (DK / 8 + DV / 8), piece = c % (DK / 8 + DV / 8);
-      const int j = j0 + r;
-      long row = -1;
-      if (j <= p1) {
-        const int page = table[j / page_size];
-        if (page < 0 || page >= num_pages) {
-          atomicOr(err, DSP_ERR_BAD_PAGE);
-          bad = 1;
-        } else {
-          row = ((long)page * G + g) * page_size + j % page_size;
-        }
+    // two threads a key row: the page is looked up once a row, the row's 16-byte pieces alternate
+    const int r = tid >> 1;
+    const int j = j0 + r;
+    long row = -1;
+    if (j <= p1) {
+      const int page = table[j / page_size];
+      if (page < 0 || page >= num_pages) {
+        atomicOr(err, DSP_ERR_BAD_PAGE);
+        bad = 1;
+      } else {
+        row = ((long)page * G + g) * page_size + j % page_size;
       }
-      const bool is_k = piece < DK / 8;
-      const int d = (is_k ? piece : piece - DK / 8) * 8;
-      bf16* dst = is_k ? ks + r * LDK + d : vs + r * LDV + d;
+    }
+    const bf16* ksrc = k_pool + row * DK;
+    const bf16* vsrc = v_pool + row * DV;
+#pragma unroll
+    for (int piece = (tid & 1); piece < DK / 8; piece += 2) {
       if (row >= 0)
-        cp16(dst, is_k ? k_pool + row * DK + d : v_pool + row * DV + d);
+        cp16(ks + r * LDK + piece * 8, ksrc + piece * 8);
       else
-        *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(ks + r * LDK + piece * 8) = make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int piece = (tid & 1); piece < DV / 8; piece += 2) {
+      if (row >= 0)
+        cp16(vs + r * LDV + piece * 8, vsrc + piece * 8);
+      else
+        *reinterpret_cast<uint4*>(vs + r * LDV + piece * 8) = make_uint4(0, 0, 0, 0);
     }
     return bad;
   };
-  int bad_now = load(0, 0);
+  int bad_now = nkt > 0 ? load(0, 0) : 0;
   asm volatile("cp.async.commit_group;\n");
 
   const int ra = warp * 16 + (lane >> 2), rb = ra + 8;  // the two rows of this thread's fragments
   const int pa = ra < rows ? pos0 + ra / group : -1, pb = rb < rows ? pos0 + rb / group : -1;
   float m[2], l[2], o[DV / 8][4];
-  m[0] = m[1] = sink ? 0.f : -INFINITY;
-  l[0] = l[1] = (sink && (lane & 3) == 0) ? 1.f : 0.f;
+  const bool with_sink = sink && split == 0;
+  m[0] = m[1] = with_sink ? 0.f : -INFINITY;
+  l[0] = l[1] = (with_sink && (lane & 3) == 0) ? 1.f : 0.f;
 #pragma unroll
   for (int i = 0; i < DV / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
 
@@ -142,7 +159,7 @@ attn_sink_mma_kernel(const bf16* __restrict__ q, long ldq, const bf16* __restric
         mma16816(s[j + 1], a, b[2], b[3]);
       }
     }
-    const int j0 = lo + kt * BN;
+    const int j0 = lo + (kt0 + kt) * BN;
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int i = 0; i < BN / 8; ++i)
@@ -203,8 +220,18 @@ attn_sink_mma_kernel(const bf16* __restrict__ q, long ldq, const bf16* __restric
   for (int h = 0; h < 2; ++h) {
     const int r = h == 0 ? ra : rb;
     if (r >= rows) continue;
+    const size_t token = (size_t)(qs + tok0 + r / group);
+    const int head = g * group + r % group;
+    if (splits > 1) {
+      const size_t part = (token * H + head) * splits + split;
+      float* dst = part_o + part * DV + (lane & 3) * 2;
+#pragma unroll
+      for (int i = 0; i < DV / 8; ++i) *reinterpret_cast<float2*>(dst + i * 8) = make_float2(o[i][2 * h], o[i][2 * h + 1]);
+      if ((lane & 3) == 0) reinterpret_cast<float2*>(part_ml)[part] = make_float2(m[h], l[h]);
+      continue;
+    }
     const float inv = l[h] > 0.f ? 1.f / l[h] : 0.f;
-    bf16* dst = out + (size_t)(qs + tok0 + r / group) * ldo + (size_t)(g * group + r % group) * DV + (lane & 3) * 2;
+    bf16* dst = out + token * ldo + (size_t)head * DV + (lane & 3) * 2;
 #pragma unroll
     for (int i = 0; i < DV / 8; ++i)
       *reinterpret_cast<uint32_t*>(dst + i * 8) = pack2(o[i][2 * h] * inv, o[i][2 * h + 1] * inv);
@@ -218,11 +245,12 @@ attn_sink_mma_kernel(const bf16* __restrict__ q, long ldq, const bf16* __restric
 // Returns 0, or: 1 launch failed, 2 unsupported sizes, 3 misaligned operands, 4 shared memory opt-in failed.
 extern "C" int DSP_CAT(dsp_attn_sink_mma_k, DSP_DK, _v, DSP_DV)(
     const void* q, long ldq, const void* k_pool, const void* v_pool, const int* page_table, int pt_stride,
-    const int* q_start, const int* ctx_len, const int* tile_seq, const int* tile_tok0, int num_tiles, void* out,
-    long ldo, int H, int G, int tpt, int page_size, int num_pages, int window, float scale, int sink, int* err,
-    cudaStream_t stream) {
+    const int* q_start, const int* ctx_len, const int* tile_seq, const int* tile_tok0, int tile_offset, int num_tiles,
+    void* out, long ldo, int H, int G, int tpt, int page_size, int num_pages, int window, float scale, int sink,
+    int splits, float* part_o, float* part_ml, int* err, cudaStream_t stream) {
   if (num_tiles == 0) return 0;
   if (G <= 0 || H % G || tpt <= 0 || tpt * (H / G) > BM || G > 65535 || page_size <= 0 || !err) return 2;
+  if (splits < 1 || splits > 32 || (splits > 1 && (!part_o || !part_ml))) return 2;
   if (((uintptr_t)q % 16) || ((uintptr_t)k_pool % 16) || ((uintptr_t)v_pool % 16) || ((uintptr_t)out % 4) || ldq % 8 || ldo % 2)
     return 3;
   const size_t smem = sizeof(bf16) * ((size_t)BM * LDK + 2 * (size_t)BN * LDK + 2 * (size_t)BN * LDV);
@@ -232,9 +260,9 @@ extern "C" int DSP_CAT(dsp_attn_sink_mma_k, DSP_DK, _v, DSP_DV)(
       return 4;
     configured = true;
   }
-  const cudaError_t e = launch_plain(attn_sink_mma_kernel, dim3(num_tiles, G), dim3(128), smem, stream, (const bf16*)q, ldq,
+  const cudaError_t e = launch_plain(attn_sink_mma_kernel, dim3(num_tiles, G, splits), dim3(128), smem, stream, (const bf16*)q, ldq,
                                      (const bf16*)k_pool, (const bf16*)v_pool, page_table, pt_stride, q_start, ctx_len,
                                      tile_seq, tile_tok0, (bf16*)out, ldo, H, G, tpt, page_size, num_pages, window,
-                                     scale * 1.4426950408889634f, sink, err);
+                                     scale * 1.4426950408889634f, sink, tile_offset, splits, part_o, part_ml, err);
   return e == cudaSuccess && cudaGetLastError() == cudaSuccess ? 0 : 1;
 }

@@ -6,7 +6,7 @@
 //                    either type); experts form `groups` equal runs of neighbours, a group's score
 //                    is its largest score, only experts of the `keep` best groups can be chosen;
 //                    the `top` largest of those are the token's experts, their scores its weights
-//                    (not renormalised).  Equal scores: the lower index wins.  One warp per token.
+//                    (not renormalised).  Equal scores: the lower index wins.  One block per token.
 //   dsp_moe_plan     counts the (token, choice) pairs per expert, lists the pairs expert by expert
 //                    and cuts every expert's run into tiles of TILE_ROWS rows.  One block.
 //   dsp_moe_product  C[c_row(i)] = act(A[a_row(i)] B_e^T) for the sorted pairs i of every expert e
@@ -20,7 +20,9 @@
 
 namespace {
 constexpr int TILE_ROWS = 32, TILE_COLS = 64, TILE_K = 32;
-constexpr int MMA_ROWS = 64, MMA_COLS = 128, MMA_K = 32, MMA_PAD = 8, MMA_STAGES = 3;
+constexpr int MMA_ROWS = 64, MMA_COLS = 128, MMA_K = 64, MMA_PAD = 8, MMA_STAGES = 4;
+constexpr int MMA_LD = MMA_K + MMA_PAD;
+constexpr size_t MMA_SMEM = sizeof(bf16) * MMA_STAGES * (MMA_ROWS + MMA_COLS) * MMA_LD;
 
 struct Best {
   float v;
@@ -45,19 +47,32 @@ __global__ void __launch_bounds__(128)
 moe_route_kernel(const void* __restrict__ h, int h_dtype, long ldh, const float* __restrict__ w, int T, int W, int E,
                  int groups, int keep, int top, int* __restrict__ ids, float* __restrict__ wts) {
   extern __shared__ float sm[];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const long t = (long)blockIdx.x * (blockDim.x >> 5) + warp;
-  if (t >= T) return;
-  float* sc = sm + (size_t)warp * (2 * E + groups);  // scores
-  float* ok = sc + E;                               // 1: may still be chosen
-  float* gb = ok + E;                               // best score of each group
-  for (int e = 0; e < E; ++e) {
-    float acc = 0.f;
-    for (int i = lane; i < W; i += 32) acc = fmaf(w[(size_t)e * W + i], ld_any(h, h_dtype, (size_t)t * ldh + i), acc);
-    acc = warp_sum(acc);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  const long t = blockIdx.x;
+  float* sc = sm;              // [E] scores
+  float* ok = sc + E;          // [E] 1: may still be chosen
+  float* gb = ok + E;          // [groups] best score of each group
+  float* hs = gb + groups;     // [W] the token's row
+  for (int i = threadIdx.x; i < W; i += blockDim.x) hs[i] = ld_any(h, h_dtype, (size_t)t * ldh + i);
+  __syncthreads();
+  // every expert's logit is the same sum whatever the block's shape: lane i takes columns i, i + 32, ...
+  // in four interleaved chains (so that four loads are in flight), added in a fixed order
+  for (int e = warp; e < E; e += warps) {
+    const float* we = w + (size_t)e * W;
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    int i = lane;
+    for (; i + 96 < W; i += 128) {
+      a0 = fmaf(we[i], hs[i], a0);
+      a1 = fmaf(we[i + 32], hs[i + 32], a1);
+      a2 = fmaf(we[i + 64], hs[i + 64], a2);
+      a3 = fmaf(we[i + 96], hs[i + 96], a3);
+    }
+    for (; i < W; i += 32) a0 = fmaf(we[i], hs[i], a0);
+    const float acc = warp_sum((a0 + a1) + (a2 + a3));
     if (lane == 0) sc[e] = acc;
   }
-  __syncwarp();
+  __syncthreads();
+  if (warp != 0) return;
   float mx = -INFINITY;
   for (int e = lane; e < E; e += 32) mx = fmaxf(mx, sc[e]);
   mx = warp_max(mx);
@@ -202,7 +217,7 @@ moe_product_kernel(const T* __restrict__ A, long lda, const int* __restrict__ a_
 
 // The same product on tensor cores (bfloat16 operands, 32-bit accumulators): a tile of up to 64
 // pairs x 128 outputs per block of four warps (2 x 2, each 32 x 64 in m16n8k16 pieces), k in
-// blocks of 32 through a ring of three cp.async stages; A rows are gathered by their indices.
+// blocks of 64 through a ring of four cp.async stages; A rows are gathered by their indices.
 // K and the row strides are multiples of 8 elements and the operands 16-byte aligned.
 __device__ __forceinline__ void cp16(void* smem, const void* gmem) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem));
@@ -226,8 +241,10 @@ moe_product_mma_kernel(const bf16* __restrict__ A, long lda, const int* __restri
                        const int* __restrict__ n_tiles, int N, int K, int act) {
   const int tile = blockIdx.x;
   if (tile >= *n_tiles) return;
-  __shared__ __align__(16) bf16 As[MMA_STAGES][MMA_ROWS][MMA_K + MMA_PAD];
-  __shared__ __align__(16) bf16 Bs[MMA_STAGES][MMA_COLS][MMA_K + MMA_PAD];
+  extern __shared__ __align__(16) unsigned char mma_smem[];
+  bf16 (*As)[MMA_ROWS][MMA_LD] = reinterpret_cast<bf16 (*)[MMA_ROWS][MMA_LD]>(mma_smem);
+  bf16 (*Bs)[MMA_COLS][MMA_LD] =
+      reinterpret_cast<bf16 (*)[MMA_COLS][MMA_LD]>(mma_smem + sizeof(bf16) * MMA_STAGES * MMA_ROWS * MMA_LD);
   __shared__ long arow[MMA_ROWS], crow[MMA_ROWS];
   const int e = tile_expert[tile], r0 = tile_row0[tile], nr = tile_rows[tile];
   const int n0 = blockIdx.y * MMA_COLS;
@@ -339,11 +356,10 @@ extern "C" int dsp_moe_route(const void* h, int h_dtype, long ldh, const float* 
   DSP_REQUIRE(E > 0 && groups > 0 && E % groups == 0 && keep > 0 && keep <= groups && top > 0 &&
                   top <= keep * (E / groups),
               "dsp_moe_route: experts=%d groups=%d keep=%d top=%d do not fit together", E, groups, keep, top);
-  const int warps = 4;
-  const size_t smem = (size_t)warps * (2 * E + groups) * sizeof(float);
-  DSP_REQUIRE(smem <= 48 * 1024, "dsp_moe_route: %d experts are more than the router kernel holds", E);
-  DSP_CUDA(launch_plain(moe_route_kernel, dim3((unsigned)((T + warps - 1) / warps)), dim3(32 * warps), smem, stream, h,
-                        h_dtype, ldh, w, T, W, E, groups, keep, top, ids, wts));
+  const size_t smem = (size_t)(2 * E + groups + W) * sizeof(float);
+  DSP_REQUIRE(smem <= 48 * 1024, "dsp_moe_route: %d experts over a width of %d are more than the router kernel holds", E, W);
+  DSP_CUDA(launch_plain(moe_route_kernel, dim3((unsigned)T), dim3(128), smem, stream, h, h_dtype, ldh, w, T, W, E,
+                        groups, keep, top, ids, wts));
   DSP_CHECK_LAUNCH("dsp_moe_route");
   return 0;
 }
@@ -376,7 +392,12 @@ extern "C" int dsp_moe_product(const void* A, int ab_dtype, long lda, const int*
                 "stride multiples of 8 (K=%d, stride %ld)", K, lda);
     dim3 mgrid(max_tiles, (N + MMA_COLS - 1) / MMA_COLS);
     DSP_REQUIRE(mgrid.y <= 65535, "dsp_moe_product: N=%d is too wide", N);
-    DSP_CUDA(launch_plain(moe_product_mma_kernel, mgrid, dim3(128), 0, stream, (const bf16*)A, lda, a_rows, a_div,
+    static bool configured = false;
+    if (!configured) {
+      DSP_CUDA(cudaFuncSetAttribute(moe_product_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MMA_SMEM));
+      configured = true;
+    }
+    DSP_CUDA(launch_plain(moe_product_mma_kernel, mgrid, dim3(128), MMA_SMEM, stream, (const bf16*)A, lda, a_rows, a_div,
                           (const bf16*)B, C, c_dtype, ldc, c_rows, tile_expert, tile_row0, tile_rows, n_tiles, N, K, act));
     DSP_CHECK_LAUNCH("dsp_moe_product (tensor cores)");
     return 0;

@@ -349,22 +349,47 @@ def sink_tokens_per_tile(group_size: int, key_dim: int, value_dim: int):
     return SINK_ROWS_PER_TILE // group_size
 
 
+def sink_choose_splits(num_single: int, num_kv_heads: int, keys: int, device=None) -> int:
+    """Key splits for the single tokens of a step: enough blocks to fill the device, at least two
+    key tiles of 64 a block, at most 16."""
+    if num_single <= 0:
+        return 1
+    tiles = max(1, -(-keys // 64) + 1)
+    want = -(-tuning.attention_target_ctas(device) // max(1, num_single * num_kv_heads))
+    return max(1, min(16, tiles // 2, want))
+
+
 def sink_attention_tiles(q, k_pool, v_pool, page_table, q_start, ctx_len, tile_seq, tile_tok0, num_tiles, out,
-                         num_heads, num_kv_heads, window, scale, sink) -> torch.Tensor:
-    """The tensor-core kernel over a tile list (``tokens per tile`` = 64 // group)."""
+                         num_heads, num_kv_heads, window, scale, sink, num_single: int = 0, splits: int = 1) -> torch.Tensor:
+    """The tensor-core kernel over a tile list (``tokens per tile`` = 64 // group).  The first
+    ``num_single`` tiles are single tokens (the first rows of the batch): with ``splits`` > 1
+    their keys are cut into that many shares, merged by the combine kernel."""
     num_pages, G, page_size, dk = k_pool.shape
     dv = v_pool.shape[3]
     assert q.dtype == k_pool.dtype == v_pool.dtype == out.dtype == torch.bfloat16
     assert k_pool.is_contiguous() and v_pool.is_contiguous() and q.stride(1) == 1 and out.stride(1) == 1
     fn = getattr(L.sink_attention_library(dk, dv), f"dsp_attn_sink_mma_k{dk}_v{dv}")
-    rc = fn(L.ptr(q), L.i64(q.stride(0)), L.ptr(k_pool), L.ptr(v_pool), L.ptr(page_table), page_table.stride(0),
-            L.ptr(q_start), L.ptr(ctx_len), L.ptr(tile_seq), L.ptr(tile_tok0), num_tiles, L.ptr(out),
-            L.i64(out.stride(0)), num_heads, num_kv_heads, SINK_ROWS_PER_TILE // (num_heads // num_kv_heads),
-            page_size, num_pages, window, L.f32(scale), int(sink), ctypes.c_void_p(_device_error_address(q.device)),
-            L.stream_handle())
-    L.LaunchCounter.n += 1
-    if rc != 0:
-        raise L.KernelError(f"dsp_attn_sink_mma_k{dk}_v{dv}: {_MMA_ERRORS.get(rc, rc)}")
+    tpt = SINK_ROWS_PER_TILE // (num_heads // num_kv_heads)
+
+    def launch(offset, count, n_splits, part_o, part_ml):
+        rc = fn(L.ptr(q), L.i64(q.stride(0)), L.ptr(k_pool), L.ptr(v_pool), L.ptr(page_table), page_table.stride(0),
+                L.ptr(q_start), L.ptr(ctx_len), L.ptr(tile_seq), L.ptr(tile_tok0), offset, count, L.ptr(out),
+                L.i64(out.stride(0)), num_heads, num_kv_heads, tpt, page_size, num_pages, window, L.f32(scale),
+                int(sink), n_splits, L.ptr(part_o), L.ptr(part_ml), ctypes.c_void_p(_device_error_address(q.device)),
+                L.stream_handle())
+        L.LaunchCounter.n += 1
+        if rc != 0:
+            raise L.KernelError(f"dsp_attn_sink_mma_k{dk}_v{dv}: {_MMA_ERRORS.get(rc, rc)}")
+
+    first = 0
+    if num_single > 0 and splits > 1:
+        part_o, part_ml = _partial_buffers(q.device, num_single * num_heads, splits, dv)
+        launch(0, num_single, splits, part_o, part_ml)
+        L.check(L.core().dsp_attn_combine(L.ptr(part_o), L.ptr(part_ml), L.ptr(out), L.i64(out.stride(0)), num_single,
+                                          num_heads, dv, splits, L.dtype_code(out.dtype), L.stream_handle()))
+        first = num_single
+    if num_tiles > first:
+        launch(first, num_tiles - first, 1, None, None)
     return out
 
 
@@ -378,8 +403,11 @@ def sink_paged_attention(ctx, q: torch.Tensor, cache, out: torch.Tensor, num_hea
     tpt = sink_tokens_per_tile(group, key_dim, value_dim)
     if q.dtype == torch.bfloat16 and tpt is not None and tpt in ctx.attention_tiles:
         tile_seq, tile_tok0, num_tiles = ctx.attention_tiles[tpt]
+        keys = min(ctx.max_ctx_len, window) if window > 0 else ctx.max_ctx_len
+        splits = sink_choose_splits(ctx.num_decode_seqs, num_kv_heads, keys, q.device)
         return sink_attention_tiles(q, cache.key_pool, cache.value_pool, cache.page_table, ctx.q_start, ctx.ctx_len,
-                                    tile_seq, tile_tok0, num_tiles, out, num_heads, num_kv_heads, window, scale, sink)
+                                    tile_seq, tile_tok0, num_tiles, out, num_heads, num_kv_heads, window, scale, sink,
+                                    num_single=ctx.num_decode_seqs, splits=splits)
     return paged_attention_generic(q, q.stride(0), cache.key_pool, cache.value_pool, cache.page_table,
                                    ctx.positions, ctx.seq_of_token, out, num_heads, num_kv_heads, key_dim,
                                    window, scale, sink=sink)

@@ -448,12 +448,14 @@ def test_sink_attention_sees_exactly_the_window(H, G, dk, dv, page, window, pool
 
 @pytest.mark.parametrize("H,G,dk,dv,page,window", [(4, 2, 16, 16, 16, 20), (18, 2, 64, 128, 32, 64), (8, 1, 128, 64, 16, 100),
                                                    (12, 2, 128, 128, 16, 0), (6, 2, 32, 16, 8, 7), (5, 5, 48, 32, 16, 33)])
-@pytest.mark.parametrize("sink", [True, False])
-def test_sink_attention_on_tensor_cores_matches_the_plain_softmax(H, G, dk, dv, page, window, sink):
+@pytest.mark.parametrize("sink,splits", [(True, 1), (False, 1), (True, 3), (False, 4), (True, 16)])
+def test_sink_attention_on_tensor_cores_matches_the_plain_softmax(H, G, dk, dv, page, window, sink, splits):
     """A step of two single tokens and a portion of a prompt whose tiles end in the middle of a key
     tile; every query is aimed at one key: the first of the request, both sides of a page border,
     the first key of its window and the one before it, its own position, the next one (stored,
-    invisible), or nothing (the sink takes the weight).  Scattered pages, NaN everywhere else."""
+    invisible), or nothing (the sink takes the weight).  Scattered pages, NaN everywhere else.
+    With ``splits`` the single tokens' keys are cut into shares (more shares than key tiles too)
+    and merged; the sink must count once."""
     from dispec_b200.ops import attention as A
     g = torch.Generator().manual_seed(H + dk)
     lens, q_lens = [3 * page + 5, 200, 9 * page + 7], [1, 1, 45]
@@ -500,7 +502,8 @@ def test_sink_attention_on_tensor_cores_matches_the_plain_softmax(H, G, dk, dv, 
     scale = 0.4
     A.sink_attention_tiles(dev(torch.cat(qs).reshape(T, -1), torch.bfloat16), dev(k_pool, torch.bfloat16),
                            dev(v_pool, torch.bfloat16), i32(tables), i32([0, 1, 2, 2 + q_lens[2]]), i32(lens),
-                           i32([s for s, _ in tiles]), i32([a for _, a in tiles]), len(tiles), out, H, G, window, scale, sink)
+                           i32([s for s, _ in tiles]), i32([a for _, a in tiles]), len(tiles), out, H, G, window, scale, sink,
+                           num_single=2, splits=splits)
     out = out.float().cpu().double().view(T, H, dv)
     assert torch.isfinite(out).all()
     at = 0
