@@ -162,6 +162,8 @@ def build_all(head_dims=(16, 32, 64, 128)) -> list[str]:
         if d in (64, 128):
             libs.append(prefill_attention_library(d))
     libs += [mixer_library(name) for name in MIXER_LIBRARIES]
+    # the attention with widths of their own for keys and values is compiled per pair of widths
+    libs += [sink_attention_library(dk, dv) for dk, dv in ((64, 64), (128, 64), (128, 128))]
     return libs
 
 

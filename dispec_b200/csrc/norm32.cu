@@ -61,6 +61,28 @@ head_norm_gate_kernel(const float* __restrict__ o, long ldo, const float* __rest
   }
 }
 
+// The same for wide heads (a "head" may be the whole row): one block per (token, head).
+__global__ void __launch_bounds__(256)
+head_norm_gate_wide_kernel(const float* __restrict__ o, long ldo, const float* __restrict__ gain,
+                           const void* __restrict__ gate, int g_dtype, long ldg, void* __restrict__ y,
+                           int y_dtype, long ldy, int H, int dv, float eps, int gate_kind) {
+  __shared__ float scratch[32];
+  const int t = blockIdx.x / H, h = blockIdx.x % H;
+  const float* row = o + (size_t)t * ldo + (size_t)h * dv;
+  float ss = 0.f;
+  for (int j = threadIdx.x; j < dv; j += blockDim.x) ss = fmaf(row[j], row[j], ss);
+  const float inv = 1.f / sqrtf(block_sum(ss, scratch) / (float)dv + eps);
+  for (int j = threadIdx.x; j < dv; j += blockDim.x) {
+    float v = row[j] * inv;
+    if (gain) v *= gain[j];
+    if (gate) {
+      const float g = ld_any(gate, g_dtype, (size_t)t * ldg + (size_t)h * dv + j);
+      v *= (gate_kind == 1 ? 1.f : g) / (1.f + expf(-g));
+    }
+    st_any(y, y_dtype, (size_t)t * ldy + (size_t)h * dv + j, v);
+  }
+}
+
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
 
 // xIELU with the two raw parameters (p, q) read from the device:
@@ -285,6 +307,12 @@ extern "C" int dsp_head_norm_gate(const float* o, long ldo, const float* gain, c
   DSP_REQUIRE(o && y && H > 0 && dv > 0, "dsp_head_norm_gate: missing operand");
   DSP_REQUIRE(gate_kind == 0 || gate_kind == 1, "dsp_head_norm_gate: unknown gate kind %d", gate_kind);
   const long pairs = (long)T * H;
+  if (dv >= 512) {
+    DSP_CUDA(launch_plain(head_norm_gate_wide_kernel, dim3((unsigned)pairs), dim3(256), 0, stream, o, ldo, gain, gate,
+                          g_dtype, ldg, y, y_dtype, ldy, H, dv, eps, gate_kind));
+    DSP_CHECK_LAUNCH("dsp_head_norm_gate");
+    return 0;
+  }
   DSP_CUDA(launch_plain(head_norm_gate_kernel, dim3((unsigned)((pairs + 3) / 4)), dim3(128), 0, stream, o,
                       ldo, gain, gate, g_dtype, ldg, y, y_dtype, ldy, T, H, dv, eps, gate_kind));
   DSP_CHECK_LAUNCH("dsp_head_norm_gate");

@@ -322,10 +322,11 @@ def test_lightning_recurrence_carries_its_state_over_cuts(H, d, dv):
         assert torch.isnan(state[1]).all() and torch.isnan(state[3]).all()
 
 
-def test_whole_row_norm_with_sigmoid_gate():
+@pytest.mark.parametrize("n", [60, 1536])
+def test_whole_row_norm_with_sigmoid_gate(n):
     from dispec_b200.ops import norm32
     g = torch.Generator().manual_seed(8)
-    o, gate, gain = torch.randn(5, 60, generator=g) * 3, torch.randn(5, 60, generator=g), torch.rand(60, generator=g) + 0.5
+    o, gate, gain = torch.randn(5, n, generator=g) * 3, torch.randn(5, n, generator=g), torch.rand(n, generator=g) + 0.5
     y = norm32.head_norm_gate(dev(o), 1, 1e-6, torch.float32, gain=dev(gain), gate=dev(gate), gate_kind="sigmoid")
     want = plain.rms_norm(o.double(), gain.double(), 1e-6) * torch.sigmoid(gate.double())
     assert (y.cpu().double() - want).abs().max() < 1e-5
