@@ -14,15 +14,17 @@
 //                    act 0: none, 1: the square of relu.  Every output is one chain of fused
 //                    multiply-adds in ascending k, so a pair's result depends on nothing but its own
 //                    row and its expert.  With `tensor_cores` (bfloat16 operands): mma.sync tiles of
-//                    64 pairs; the plan must have been made for tiles of that many rows.
+//                    64 pairs (1) or 128 pairs (2); the plan must have been made for tiles of that many rows.
 //   dsp_moe_combine  y[t] = sum_k weight[t, k] * P[t * top + k], in ascending k.
 #include "common.cuh"
 
 namespace {
 constexpr int TILE_ROWS = 32, TILE_COLS = 64, TILE_K = 32;
-constexpr int MMA_ROWS = 64, MMA_COLS = 128, MMA_K = 64, MMA_PAD = 8, MMA_STAGES = 4;
+// the tensor-core product comes in two shapes: 64 rows x 4 stages (few rows an expert: decoding)
+// and 128 rows x 3 stages (many rows an expert: prompts)
+constexpr int MMA_ROWS = 64, MMA_ROWS_WIDE = 128, MMA_COLS = 128, MMA_K = 64, MMA_PAD = 8;
 constexpr int MMA_LD = MMA_K + MMA_PAD;
-constexpr size_t MMA_SMEM = sizeof(bf16) * MMA_STAGES * (MMA_ROWS + MMA_COLS) * MMA_LD;
+constexpr size_t mma_smem_bytes(int rows, int stages) { return sizeof(bf16) * stages * (rows + MMA_COLS) * MMA_LD; }
 
 struct Best {
   float v;
@@ -215,9 +217,10 @@ moe_product_kernel(const T* __restrict__ A, long lda, const int* __restrict__ a_
 }
 
 
-// The same product on tensor cores (bfloat16 operands, 32-bit accumulators): a tile of up to 64
-// pairs x 128 outputs per block of four warps (2 x 2, each 32 x 64 in m16n8k16 pieces), k in
-// blocks of 64 through a ring of four cp.async stages; A rows are gathered by their indices.
+// The same product on tensor cores (bfloat16 operands, 32-bit accumulators): a tile of up to ROWS
+// pairs x 128 outputs per block of ROWS / 16 warps (ROWS / 32 x 2, each 32 x 64 in m16n8k16 pieces),
+// k in blocks of 64 through a ring of STAGES cp.async stages (two blocks an SM); A rows are
+// gathered by their indices.
 // K and the row strides are multiples of 8 elements and the operands 16-byte aligned.
 __device__ __forceinline__ void cp16(void* smem, const void* gmem) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem));
@@ -233,7 +236,8 @@ __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], 
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-__global__ void __launch_bounds__(128)
+template <int ROWS, int STAGES>
+__global__ void __launch_bounds__(ROWS * 2, 2)
 moe_product_mma_kernel(const bf16* __restrict__ A, long lda, const int* __restrict__ a_rows, int a_div,
                        const bf16* __restrict__ B, void* __restrict__ C, int c_dtype, long ldc,
                        const int* __restrict__ c_rows, const int* __restrict__ tile_expert,
@@ -242,15 +246,15 @@ moe_product_mma_kernel(const bf16* __restrict__ A, long lda, const int* __restri
   const int tile = blockIdx.x;
   if (tile >= *n_tiles) return;
   extern __shared__ __align__(16) unsigned char mma_smem[];
-  bf16 (*As)[MMA_ROWS][MMA_LD] = reinterpret_cast<bf16 (*)[MMA_ROWS][MMA_LD]>(mma_smem);
+  bf16 (*As)[ROWS][MMA_LD] = reinterpret_cast<bf16 (*)[ROWS][MMA_LD]>(mma_smem);
   bf16 (*Bs)[MMA_COLS][MMA_LD] =
-      reinterpret_cast<bf16 (*)[MMA_COLS][MMA_LD]>(mma_smem + sizeof(bf16) * MMA_STAGES * MMA_ROWS * MMA_LD);
-  __shared__ long arow[MMA_ROWS], crow[MMA_ROWS];
+      reinterpret_cast<bf16 (*)[MMA_COLS][MMA_LD]>(mma_smem + sizeof(bf16) * STAGES * ROWS * MMA_LD);
+  __shared__ long arow[ROWS], crow[ROWS];
   const int e = tile_expert[tile], r0 = tile_row0[tile], nr = tile_rows[tile];
   const int n0 = blockIdx.y * MMA_COLS;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int wm = warp >> 1, wn = warp & 1;  // the warp's 32 rows and 64 columns of the tile
-  if (tid < MMA_ROWS) {
+  if (tid < ROWS) {
     const int i = r0 + tid;
     arow[tid] = tid < nr ? (a_rows ? (long)(a_rows[i] / a_div) : (long)i) : -1;
     crow[tid] = tid < nr ? (c_rows ? (long)c_rows[i] : (long)i) : -1;
@@ -258,7 +262,7 @@ moe_product_mma_kernel(const bf16* __restrict__ A, long lda, const int* __restri
   __syncthreads();
   const bf16* Be = B + (size_t)e * N * K;
   auto load = [&](int stage, int k0) {
-    for (int c = tid; c < MMA_ROWS * (MMA_K / 8); c += 128) {
+    for (int c = tid; c < ROWS * (MMA_K / 8); c += (ROWS * 2)) {
       const int r = c / (MMA_K / 8), k = (c % (MMA_K / 8)) * 8;
       bf16* dst = &As[stage][r][k];
       if (arow[r] >= 0 && k0 + k < K)
@@ -266,7 +270,7 @@ moe_product_mma_kernel(const bf16* __restrict__ A, long lda, const int* __restri
       else
         *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
     }
-    for (int c = tid; c < MMA_COLS * (MMA_K / 8); c += 128) {
+    for (int c = tid; c < MMA_COLS * (MMA_K / 8); c += (ROWS * 2)) {
       const int n = c / (MMA_K / 8), k = (c % (MMA_K / 8)) * 8;
       bf16* dst = &Bs[stage][n][k];
       if (n0 + n < N && k0 + k < K)
@@ -278,20 +282,20 @@ moe_product_mma_kernel(const bf16* __restrict__ A, long lda, const int* __restri
   };
   float acc[2][8][4] = {};
   const int nk = (K + MMA_K - 1) / MMA_K;
-  for (int s = 0; s < MMA_STAGES - 1; ++s) {
+  for (int s = 0; s < STAGES - 1; ++s) {
     if (s < nk)
       load(s, s * MMA_K);
     else
       asm volatile("cp.async.commit_group;\n");
   }
   for (int kt = 0; kt < nk; ++kt) {
-    asm volatile("cp.async.wait_group %0;\n" ::"n"(MMA_STAGES - 2));
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(STAGES - 2));
     __syncthreads();  // stage kt has landed for everyone; stage kt - 1 has been read by everyone
-    if (kt + MMA_STAGES - 1 < nk)
-      load((kt + MMA_STAGES - 1) % MMA_STAGES, (kt + MMA_STAGES - 1) * MMA_K);
+    if (kt + STAGES - 1 < nk)
+      load((kt + STAGES - 1) % STAGES, (kt + STAGES - 1) * MMA_K);
     else
       asm volatile("cp.async.commit_group;\n");
-    const int st = kt % MMA_STAGES;
+    const int st = kt % STAGES;
 #pragma unroll
     for (int kk = 0; kk < MMA_K; kk += 16) {
       uint32_t a[2][4];
@@ -347,7 +351,7 @@ moe_combine_kernel(const float* __restrict__ P, long ldp, const float* __restric
 }  // namespace
 
 // Rows of a tile of dsp_moe_product: the tensor-core kernel's (bfloat16) or the 32-bit kernel's.
-extern "C" int dsp_moe_tile_rows(int tensor_cores) { return tensor_cores ? MMA_ROWS : TILE_ROWS; }
+extern "C" int dsp_moe_tile_rows(int tensor_cores) { return tensor_cores == 2 ? MMA_ROWS_WIDE : tensor_cores ? MMA_ROWS : TILE_ROWS; }
 
 extern "C" int dsp_moe_route(const void* h, int h_dtype, long ldh, const float* w, int T, int W, int E, int groups,
                              int keep, int top, int* ids, float* wts, cudaStream_t stream) {
@@ -368,7 +372,7 @@ extern "C" int dsp_moe_plan(const int* ids, int n_pairs, int E, int rows_per_til
                             int* tile_expert, int* tile_row0, int* tile_rows, int* n_tiles, int max_tiles,
                             cudaStream_t stream) {
   DSP_REQUIRE(ids && offsets && sorted_pair && tile_expert && tile_row0 && tile_rows && n_tiles, "dsp_moe_plan: missing operand");
-  DSP_REQUIRE(rows_per_tile == TILE_ROWS || rows_per_tile == MMA_ROWS, "dsp_moe_plan: tiles of %d rows", rows_per_tile);
+  DSP_REQUIRE(rows_per_tile == TILE_ROWS || rows_per_tile == MMA_ROWS || rows_per_tile == MMA_ROWS_WIDE, "dsp_moe_plan: tiles of %d rows", rows_per_tile);
   DSP_REQUIRE(max_tiles >= n_pairs / rows_per_tile + E, "dsp_moe_plan: room for %d tiles, %d may be needed", max_tiles,
               n_pairs / rows_per_tile + E);
   const size_t smem = (size_t)(3 * E + 1) * sizeof(int);
@@ -394,11 +398,20 @@ extern "C" int dsp_moe_product(const void* A, int ab_dtype, long lda, const int*
     DSP_REQUIRE(mgrid.y <= 65535, "dsp_moe_product: N=%d is too wide", N);
     static bool configured = false;
     if (!configured) {
-      DSP_CUDA(cudaFuncSetAttribute(moe_product_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MMA_SMEM));
+      DSP_CUDA(cudaFuncSetAttribute(moe_product_mma_kernel<MMA_ROWS, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    (int)mma_smem_bytes(MMA_ROWS, 4)));
+      DSP_CUDA(cudaFuncSetAttribute(moe_product_mma_kernel<MMA_ROWS_WIDE, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    (int)mma_smem_bytes(MMA_ROWS_WIDE, 3)));
       configured = true;
     }
-    DSP_CUDA(launch_plain(moe_product_mma_kernel, mgrid, dim3(128), MMA_SMEM, stream, (const bf16*)A, lda, a_rows, a_div,
-                          (const bf16*)B, C, c_dtype, ldc, c_rows, tile_expert, tile_row0, tile_rows, n_tiles, N, K, act));
+    if (tensor_cores == 2)
+      DSP_CUDA(launch_plain(moe_product_mma_kernel<MMA_ROWS_WIDE, 3>, mgrid, dim3(MMA_ROWS_WIDE * 2), mma_smem_bytes(MMA_ROWS_WIDE, 3),
+                            stream, (const bf16*)A, lda, a_rows, a_div, (const bf16*)B, C, c_dtype, ldc, c_rows, tile_expert,
+                            tile_row0, tile_rows, n_tiles, N, K, act));
+    else
+      DSP_CUDA(launch_plain(moe_product_mma_kernel<MMA_ROWS, 4>, mgrid, dim3(MMA_ROWS * 2), mma_smem_bytes(MMA_ROWS, 4), stream,
+                            (const bf16*)A, lda, a_rows, a_div, (const bf16*)B, C, c_dtype, ldc, c_rows, tile_expert,
+                            tile_row0, tile_rows, n_tiles, N, K, act));
     DSP_CHECK_LAUNCH("dsp_moe_product (tensor cores)");
     return 0;
   }

@@ -41,7 +41,7 @@ class ExpertPlan:
     max_tiles: int
     num_pairs: int
     top: int
-    tensor_cores: bool  # tiles of as many rows as the tensor-core kernel takes
+    tensor_cores: int  # 0: the 32-bit kernel; 1, 2: the tensor-core kernel with tiles of 64, 128 rows
 
 
 def tensor_cores_supported(dtype: torch.dtype, *inner_sizes: int) -> bool:
@@ -49,11 +49,15 @@ def tensor_cores_supported(dtype: torch.dtype, *inner_sizes: int) -> bool:
     return dtype == torch.bfloat16 and all(k % 8 == 0 for k in inner_sizes)
 
 
+WIDE_TILES_FROM = 96  # (token, choice) pairs per expert on average from which tiles of 128 rows pay
+
+
 def plan(ids: torch.Tensor, num_experts: int, tensor_cores: bool = False) -> ExpertPlan:
     T, top = ids.shape
     n = T * top
     lib = _lib()
-    rows = int(lib.dsp_moe_tile_rows(int(tensor_cores)))
+    tensor_cores = (2 if n >= WIDE_TILES_FROM * num_experts else 1) if tensor_cores else 0
+    rows = int(lib.dsp_moe_tile_rows(tensor_cores))
     max_tiles = n // rows + num_experts
     dev = ids.device
     sorted_pair = torch.empty(max(n, 1), dtype=torch.int32, device=dev)
