@@ -35,18 +35,30 @@ def test_key_ranges_fill_the_gpu_for_one_long_request():
     assert A.choose_outer(64, 2, 32768, A.choose_splits(64, 2, 32768, SLOTS), SLOTS) == 1  # many rows need none
 
 
-@pytest.mark.parametrize("limit", [512, 2048, 5000, 40000, 1 << 21])
+@pytest.mark.parametrize("limit", [512, 2048, 5000, 40000, 1 << 21, 1 << 30])
 def test_context_class_of_a_captured_step(limit):
+    """The listed classes, beyond them doublings of the last one (a model whose cache groups all
+    have windows has no longest request of its own: its limit is 2^30, and a captured step's page
+    tables must not be that wide), never more than the limit."""
     runner = SimpleNamespace(max_model_len=limit)
+    classes = list(GRAPH_CONTEXT_CLASSES)
+    while classes[-1] < limit:
+        classes.append(classes[-1] * 2)
     seen = set()
-    for n in (1, 2047, 2048, 2049, 8192, 8193, 32768, 40000, 131072, 131073, 600000):
+    for n in (1, 2047, 2048, 2049, 8192, 8193, 32768, 40000, 131072, 131073, 600000, 3000000):
         if n > limit:
             continue
         entries = [SeqEntry("a", [0], 5, [0]), SeqEntry("b", [0], n - 1, [0])]
         bound = ModelRunner._context_class(runner, entries)
         assert n <= bound <= limit  # the class holds the step's longest request
-        assert bound == limit or bound in GRAPH_CONTEXT_CLASSES
-        smaller = [c for c in GRAPH_CONTEXT_CLASSES if n <= c < limit]
+        smaller = [c for c in classes if n <= c < limit]
         assert bound == (min(smaller) if smaller else limit)  # and is the smallest that does
+        assert bound < 2 * max(n, GRAPH_CONTEXT_CLASSES[0]) or bound in GRAPH_CONTEXT_CLASSES or bound == limit
         seen.add(bound)
-    assert len(seen) <= len(GRAPH_CONTEXT_CLASSES) + 1
+    assert len(seen) <= len(GRAPH_CONTEXT_CLASSES) + 3
+
+
+def test_page_tables_of_a_captured_step_follow_its_context_class():
+    runner = SimpleNamespace(max_model_len=1 << 30, page_size=16, _group_windows=[0, 96], _group_pages=[100, 100])
+    assert ModelRunner._graph_pages(runner, 2048) == [100, 128]  # a full group: its pool; a window group: the context
+    assert ModelRunner._graph_pages(runner, 1024) == [64, 64]
